@@ -2,3 +2,4 @@
 from . import gpt2  # noqa: F401
 from . import pedorax  # noqa: F401
 from . import putelix  # noqa: F401
+from . import roritar  # noqa: F401

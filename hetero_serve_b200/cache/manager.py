@@ -65,11 +65,14 @@ def chain_hashes(token_ids: Sequence[int], page_size: int) -> list[int]:
 class GroupSpec:
     """One page group: ``window == 0`` keeps every position, ``window == w`` the last w;
     ``chunk == c`` keeps the positions of the chunk of c the request's next token falls in
-    (chunks counted from position 0)."""
+    (chunks counted from position 0).  ``stride == s > 1``: the group keeps one row for every
+    complete block of s positions (all of them: no window), so a page holds ``page_size``
+    blocks."""
 
     window: int = 0
     chunk: int = 0
     num_pages: int | None = None      # None → the manager's default
+    stride: int = 1
 
 
 class PagePool:
@@ -216,7 +219,8 @@ class CacheManager:
         # a shared prefix is only sound when every group still holds it and no mixer keeps
         # state beside the pages
         self.prefix_cache = (prefix_cache and not has_state and len(self.groups) > 0
-                             and all(g.window == 0 and g.chunk == 0 for g in self.groups))
+                             and all(g.window == 0 and g.chunk == 0 and g.stride == 1
+                                     for g in self.groups))
         self.pools = [PagePool(g.num_pages or num_pages, self.prefix_cache) for g in self.groups]
         self.max_requests = max_requests
         self._free_slots = list(range(max_requests - 1, -1, -1))
@@ -256,7 +260,11 @@ class CacheManager:
     def pages_free(self, group: int = 0) -> int:
         return self.pools[group].num_free
 
-    def pages_for(self, n_tokens: int) -> int:
+    def pages_for(self, n_tokens: int, group: int | None = None) -> int:
+        """Pages that hold the rows of positions < n_tokens (of a group that keeps one row per
+        block of positions: the rows of the complete blocks)."""
+        if group is not None and self.groups[group].stride > 1:
+            n_tokens = n_tokens // self.groups[group].stride
         return -(-n_tokens // self.page_size)
 
     def max_pages_per_request(self, max_positions: int) -> int:
@@ -328,8 +336,7 @@ class CacheManager:
     def pages_needed(self, req_id, new_len: int) -> list[int]:
         """Fresh pages each group must supply so that positions < new_len have a page."""
         req = self._get(req_id)
-        want = self.pages_for(new_len)
-        return [max(0, want - len(t)) for t in req.tables]
+        return [max(0, self.pages_for(new_len, gi) - len(t)) for gi, t in enumerate(req.tables)]
 
     def can_reserve(self, req_id, new_len: int) -> bool:
         need = self.pages_needed(req_id, new_len)
@@ -355,7 +362,7 @@ class CacheManager:
         before the reservation): undoes a :meth:`reserve` whose step did not run."""
         req = self._get(req_id)
         for gi, (n, pool) in enumerate(zip(lengths, self.pools)):
-            if self.pages_for(req.length) > n:
+            if self.pages_for(req.length, gi) > n:
                 raise CacheError("unreserve below the resident positions")
             table = req.tables[gi]
             while len(table) > n:
@@ -369,7 +376,7 @@ class CacheManager:
         req = self._get(req_id)
         if new_len < req.length:
             raise CacheError("a request's length cannot shrink")
-        if any(self.pages_for(new_len) > len(t) for t in req.tables):
+        if any(self.pages_for(new_len, gi) > len(t) for gi, t in enumerate(req.tables)):
             raise CacheError("commit beyond the reserved pages")
         req.length = new_len
         for gi, g in enumerate(self.groups):
@@ -437,7 +444,7 @@ class CacheManager:
                "hits": self.hit_tokens, "misses": self.miss_tokens, "groups": []}
         for g, pool in zip(self.groups, self.pools):
             out["groups"].append({
-                "window": g.window, "chunk": g.chunk, "num_blocks": pool.num_pages, "used": pool.num_used,
+                "window": g.window, "chunk": g.chunk, "stride": g.stride, "num_blocks": pool.num_pages, "used": pool.num_used,
                 "free": pool.num_free, "cached_blocks": len(pool._hash_to_page),
                 "evictable": len(pool._evictable), "evictions": pool.evictions,
                 "utilisation": round(pool.num_used / pool.num_pages, 4)})

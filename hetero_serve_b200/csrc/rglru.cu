@@ -1,0 +1,174 @@
+// The real-gated linear recurrent unit: short convolution, gates, decay and the recurrence.
+//
+//   rglru_conv   u[t, c] = cb[c] + sum_j cw[c, taps-1-j] * xb[t-j, c]   (causal; rows before the
+//                portion's first token come from the request's history of taps-1 inputs, which
+//                is zero for a new request)
+//   rglru_scan   r = sigmoid(z_r + b_r), i = sigmoid(z_i + b_i)    (z: the block-diagonal
+//                products of u, columns [part][r | i][n])
+//                log a = -scale * r * rate[c];  a = exp(log a)
+//                S <- a S + sqrt(1 - a^2) i u;   out = S * gelu_tanh(y)
+//                then the state and the convolution's history are stored for the next step.
+//
+// Everything here is float32 (only `out`, the input of the output projection, is written in
+// the compute type).  The recurrence of one (request, channel) is linear, S <- a S + d, so the
+// portion is cut into up to RG_PARTS segments of equal length: every segment is first reduced
+// to its pair (product of a, result from zero), the carries are chained in index order, and
+// the segment is walked again from its carry.  The cut depends on the portion's length only;
+// sqrt(1 - a^2) is formed as sqrt(-expm1(2 log a)), which keeps its digits when a is near 1.
+#include "common.cuh"
+
+namespace hs {
+
+constexpr int RG_CH = 32;        // channels a block covers (one a lane)
+constexpr int RG_PARTS = 16;     // segments a portion is cut into (one a warp)
+constexpr int RG_MIN_SEG = 8;    // shortest segment: short portions use fewer warps
+
+__global__ void __launch_bounds__(256)
+rglru_conv_kernel(float* __restrict__ u, const float* __restrict__ proj, int proj_stride,
+                  int x_off, const float* __restrict__ cw, const float* __restrict__ cb,
+                  const float* __restrict__ state, int state_stride,
+                  const int* __restrict__ tok_req, const int* __restrict__ req_start,
+                  const int* __restrict__ req_slot, int C, int taps) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = tok_req[t];
+  if (r < 0 || c >= C) return;
+  const int local = t - req_start[r];
+  const float* hist = state + (size_t)req_slot[r] * state_stride + C;     // [taps-1][C]
+  float acc = cb[c];
+  for (int j = 0; j < taps; ++j) {
+    const int back = local - j;
+    const float v = back >= 0 ? proj[(size_t)(t - j) * proj_stride + x_off + c]
+                              : hist[(size_t)(taps - 1 + back) * C + c];
+    acc = fmaf(cw[(size_t)c * taps + (taps - 1 - j)], v, acc);
+  }
+  u[(size_t)t * C + c] = acc;
+}
+
+struct RgStep { float a, d; };
+
+__device__ __forceinline__ RgStep rg_step(float zr, float zi, float uu, float rate, float scale) {
+  const float rg = 1.0f / (1.0f + expf(-zr));
+  const float ig = 1.0f / (1.0f + expf(-zi));
+  const float log_a = -scale * rg * rate;
+  RgStep s;
+  s.a = expf(log_a);
+  s.d = sqrtf(-expm1f(2.0f * log_a)) * ig * uu;
+  return s;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(RG_CH * RG_PARTS)
+rglru_scan_kernel(TO* __restrict__ out, float* __restrict__ state, int state_stride,
+                  const float* __restrict__ u, const float* __restrict__ z,
+                  const float* __restrict__ proj, int proj_stride, int y_off, int x_off,
+                  const float* __restrict__ b_gates, const float* __restrict__ rate,
+                  const int* __restrict__ req_start, const int* __restrict__ req_len,
+                  const int* __restrict__ req_slot, int C, int n_per, int taps, float scale) {
+  __shared__ float s_a[RG_PARTS][RG_CH], s_d[RG_PARTS][RG_CH];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int n = req_len[r];
+  if (n <= 0) return;
+  const int t0 = req_start[r];
+  const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
+  const int c = blockIdx.x * RG_CH + lane;
+  const bool live = c < C;
+  int seg = (n + RG_PARTS - 1) / RG_PARTS;
+  if (seg < RG_MIN_SEG) seg = RG_MIN_SEG;
+  const int lo = part * seg, hi = min(n, lo + seg);
+  // column of this channel's gate logits: [part of the channels][r | i][n_per]
+  const int blk = live ? c / n_per : 0;
+  const int zc = blk * 2 * n_per + (c - blk * n_per);
+  float br = 0.f, bi = 0.f, rt = 0.f;
+  if (live) { br = b_gates[zc]; bi = b_gates[zc + n_per]; rt = rate[c]; }
+  float* st = state + (size_t)req_slot[r] * state_stride;
+  // pass 1: the segment as one step (A, D): S_out = A * S_in + D.  A portion that fits into
+  // one segment is walked once, in pass 2.
+  const bool single = n <= seg;
+  const float S0 = live ? st[c] : 0.f;          // read before the barrier: the last segment's
+  float A = 1.f, D = 0.f;                        // owner stores the new state behind it
+  if (live && !single) {
+    for (int i = lo; i < hi; ++i) {
+      const size_t t = (size_t)(t0 + i);
+      const RgStep s = rg_step(z[t * 2 * C + zc] + br, z[t * 2 * C + zc + n_per] + bi,
+                               u[t * C + c], rt, scale);
+      A *= s.a;
+      D = fmaf(s.a, D, s.d);
+    }
+  }
+  s_a[part][lane] = A;
+  s_d[part][lane] = D;
+  __syncthreads();
+  if (!live || lo >= n) return;
+  // pass 2: the carries of the segments before, in index order, then the segment itself
+  float S = S0;
+  for (int p = 0; p < part; ++p) S = fmaf(s_a[p][lane], S, s_d[p][lane]);
+  for (int i = lo; i < hi; ++i) {
+    const size_t t = (size_t)(t0 + i);
+    const RgStep s = rg_step(z[t * 2 * C + zc] + br, z[t * 2 * C + zc + n_per] + bi,
+                             u[t * C + c], rt, scale);
+    S = fmaf(s.a, S, s.d);
+    out[t * C + c] = from_f<TO>(S * gelu_tanh(proj[t * proj_stride + y_off + c]));
+  }
+  if (hi == n) {
+    st[c] = S;
+    // the last taps-1 inputs of the convolution, oldest first: old history, then this portion
+    float* hist = st + C;
+    for (int k = 0; k < taps - 1; ++k) {
+      const int idx = n + k;             // place in (old history ++ portion)
+      hist[(size_t)k * C + c] = idx < taps - 1
+          ? hist[(size_t)idx * C + c]
+          : proj[(size_t)(t0 + idx - (taps - 1)) * proj_stride + x_off + c];
+    }
+  }
+}
+
+}  // namespace hs
+
+HS_EXPORT int hs_rglru_conv(float* u, const float* proj, int proj_stride, int x_off,
+                            const float* cw, const float* cb, const float* state,
+                            int state_stride, const int* tok_req, const int* req_start,
+                            const int* req_slot, int n_tokens, int C, int taps, void* stream) {
+  if (!u || !proj || !cw || !cb || !state || !tok_req || !req_start || !req_slot)
+    return HS_ERR_ARGUMENT;
+  if (C <= 0 || taps < 1 || state_stride < C * taps) return HS_ERR_UNSUPPORTED;
+  if (n_tokens <= 0) return HS_OK;
+  if (n_tokens > 65535) return HS_ERR_TOO_LARGE;
+  cudaError_t e = hs_launch(hs::rglru_conv_kernel, dim3((C + 255) / 256, n_tokens), dim3(256), 0,
+                            (cudaStream_t)stream, hs_pdl_enabled(), u, proj, proj_stride, x_off,
+                            cw, cb, state, state_stride, tok_req, req_start, req_slot, C, taps);
+  return e == cudaSuccess ? HS_OK : (int)e;
+}
+
+HS_EXPORT int hs_rglru_scan(void* out, float* state, int state_stride, const float* u,
+                            const float* z, const float* proj, int proj_stride, int y_off,
+                            int x_off, const float* b_gates, const float* rate,
+                            const int* req_start, const int* req_len, const int* req_slot,
+                            int n_requests, int C, int blocks, int taps, float scale,
+                            int out_dtype, void* stream) {
+  if (!out || !state || !u || !z || !proj || !b_gates || !rate || !req_start || !req_len ||
+      !req_slot)
+    return HS_ERR_ARGUMENT;
+  if (C <= 0 || blocks <= 0 || C % blocks || taps < 1 || state_stride < C * taps)
+    return HS_ERR_UNSUPPORTED;
+  if (n_requests <= 0) return HS_OK;
+  if (n_requests > 65535) return HS_ERR_TOO_LARGE;
+  const dim3 grid((C + hs::RG_CH - 1) / hs::RG_CH, n_requests), block(hs::RG_CH * hs::RG_PARTS);
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+  if (out_dtype == HS_DT_BF16)
+    e = hs_launch(hs::rglru_scan_kernel<__nv_bfloat16>, grid, block, 0, st, hs_pdl_enabled(),
+                  (__nv_bfloat16*)out, state, state_stride, u, z, proj, proj_stride, y_off, x_off,
+                  b_gates, rate, req_start, req_len, req_slot, C, C / blocks, taps, scale);
+  else if (out_dtype == HS_DT_F32)
+    e = hs_launch(hs::rglru_scan_kernel<float>, grid, block, 0, st, hs_pdl_enabled(),
+                  (float*)out, state, state_stride, u, z, proj, proj_stride, y_off, x_off,
+                  b_gates, rate, req_start, req_len, req_slot, C, C / blocks, taps, scale);
+  else
+    return HS_ERR_UNSUPPORTED;
+  return e == cudaSuccess ? HS_OK : (int)e;
+}

@@ -186,10 +186,10 @@ class Scheduler:
             bad = [t for t in request.prompt_ids if not 0 <= t < self.vocab_size]
             if bad:
                 raise RequestRefused(f"token id {bad[0]} is outside [0, {self.vocab_size})")
-        for pool in self.manager.pools:
-            if self.manager.pages_for(n + 1) > pool.num_pages:
+        for gi, pool in enumerate(self.manager.pools):
+            if self.manager.pages_for(n + 1, gi) > pool.num_pages:
                 raise RequestRefused(
-                    f"the prompt needs {self.manager.pages_for(n + 1)} pages, the pool has "
+                    f"the prompt needs {self.manager.pages_for(n + 1, gi)} pages, the pool has "
                     f"{pool.num_pages}")
         seq = SequenceState(request=request, t_submit=self.clock())
         self.waiting.append(seq)

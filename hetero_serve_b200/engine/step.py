@@ -106,6 +106,7 @@ class CacheView:
     num_pages: int
     writes: bool
     group: int
+    coarse: "CacheView | None" = None   # the companion group of one row per block of positions
 
 
 class Layout:
@@ -185,8 +186,15 @@ class StepContext:
         model, rn = self.runner.model, self.runner
         gi, k = model.entry_location[call.cache]
         pool = rn.storage.entry_pool(gi, k)
+        coarse = None
+        if call.cache in getattr(model, "coarse_location", {}):
+            cg, ck = model.coarse_location[call.cache]
+            cpool = rn.storage.entry_pool(cg, ck)
+            coarse = CacheView(pool=cpool, table=self.tables[cg], page_size=rn.manager.page_size,
+                               num_pages=cpool.shape[0], writes=call.writes_cache, group=cg)
         return CacheView(pool=pool, table=self.tables[gi], page_size=rn.manager.page_size,
-                         num_pages=pool.shape[0], writes=call.writes_cache, group=gi)
+                         num_pages=pool.shape[0], writes=call.writes_cache, group=gi,
+                         coarse=coarse)
 
     def state(self) -> torch.Tensor:
         """State tensor ``[slots, ...]`` of the mixer running now; rows are indexed with
@@ -245,8 +253,14 @@ class Runner:
         self.dtype = dtype
         if model.dtype != dtype:
             raise StepError("the model was bound with another dtype than the runner's")
+        # a group that keeps one row per block of positions needs that much less of the pool
+        # (a page more per request for the blocks of its last, partly filled page)
         self.manager = CacheManager(
-            [GroupSpec(window=g.window, chunk=getattr(g, "chunk", 0)) for g in model.cache_groups], num_pages, page_size,
+            [GroupSpec(window=g.window, chunk=getattr(g, "chunk", 0),
+                       stride=getattr(g, "stride", 1),
+                       num_pages=(-(-num_pages // g.stride) + max_requests
+                                  if getattr(g, "stride", 1) > 1 else None))
+             for g in model.cache_groups], num_pages, page_size,
             max_requests, prefix_cache=prefix_cache, has_state=bool(model.state_shapes))
         self.storage = CacheStorage(model, self.manager, dtype, self.device)
         self.manager.on_open = self._clear_slot
@@ -261,7 +275,8 @@ class Runner:
         # an architecture without a limit of its own can hold what the pool can
         self.max_positions = model.spec.max_positions or min(num_pages * page_size,
                                                              UNBOUNDED_MODEL_POSITIONS)
-        self.max_pages = [self.manager.pages_for(self.max_positions) for _ in model.cache_groups]
+        self.max_pages = [max(1, self.manager.pages_for(self.max_positions, gi))
+                          for gi in range(len(model.cache_groups))]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # the token each request sampled last, by state slot: what FROM_DEVICE reads
         self.feedback = torch.zeros(max(1, max_requests), dtype=torch.int32, device=self.device)

@@ -21,6 +21,8 @@ import torch
 from . import build as _build
 
 ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2, "relu2": 3, "silu": 4}
+# activations with learned numbers (how many): applied by ``learned_act`` between two linears
+LEARNED_ACTIVATIONS = {"xielu": 2}
 EXPERT_ACTIVATIONS = {"clamped": 0, "silu": 1}
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 

@@ -50,13 +50,18 @@ class CacheRequest:
     keys and values, for ordinary attention; one for a mixer that keeps a single shared
     vector per token), all of them (``window == 0``) or the last ``window`` positions.  With
     ``chunk`` a query reads only keys of its own chunk of that many positions (chunks counted
-    from position 0): the rows of chunks that have passed are never read again."""
+    from position 0): the rows of chunks that have passed are never read again.  With
+    ``pool`` the mixer also keeps, for the whole sequence, one row of the same shape for every
+    block of that many positions (block b: positions b * pool .. b * pool + pool - 1, written
+    once the block is complete); these rows live in a companion page group whose pages hold
+    ``page_size`` blocks each, and reach the mixer as ``cache.coarse``."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
     planes: int = 2
     chunk: int = 0
+    pool: int = 0
 
 
 class Part:

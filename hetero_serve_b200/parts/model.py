@@ -139,9 +139,51 @@ class OutputNormBlock(Block):
         ctx.stream_copy_fresh = low
 
 
+class SandwichNormBlock(Block):
+    """Norms before AND behind each sublayer:
+
+        x += norm1b(mixer(norm1(x)));  x += norm2b(feed_forward(norm2(x)))
+
+    A sublayer's output goes to a float32 block of its own (as under ``output_norm``); the norm
+    behind it is added into the stream by ``add_normed``, which in the same launch forms the
+    rows of the norm in front of the feed-forward.  A layer may leave ``norm2``,
+    ``feed_forward`` and ``norm2b`` out (all or none): it then ends after the mixer."""
+
+    slots = {"norm1": "norm", "mixer": "mixer", "norm1b": "norm", "norm2": "norm",
+             "feed_forward": "feed_forward", "norm2b": "norm"}
+    optional = ("norm2", "feed_forward", "norm2b")
+
+    def __init__(self, spec: LayerSpec):
+        super().__init__(spec)
+        present = [getattr(self, n) is not None for n in self.optional]
+        if any(present) != all(present):
+            raise ValueError("arrangement 'sandwich_norm': norm2, feed_forward and norm2b "
+                             "come together")
+        for name in ("norm1b", "norm2b"):
+            part = getattr(self, name)
+            if part is not None and not hasattr(part, "add_normed"):
+                raise ValueError(f"arrangement 'sandwich_norm': {name} of kind {part.kind!r} "
+                                 f"cannot be applied to a sublayer's output (no add_normed)")
+        self.has_ff = self.feed_forward is not None
+
+    def forward(self, ctx, x, cache):
+        T, W = x.shape
+        h = ctx.buffer("normed", (T, W), ctx.dtype)
+        y = ctx.buffer("sublayer_out", (T, W), torch.float32)
+        self.norm1.forward(ctx, h, x)
+        out = OutputNormBlock._run(self.mixer, ctx, h, y, cache)
+        if not self.has_ff:
+            self.norm1b.add_normed(ctx, x, out)
+            return
+        self.norm1b.add_normed(ctx, x, out, then=(self.norm2, h))
+        out = OutputNormBlock._run(self.feed_forward, ctx, h, y)
+        self.norm2b.add_normed(ctx, x, out)
+
+
 _ARRANGEMENTS: dict[str, Callable[[LayerSpec], Block]] = {"pre_norm": PreNormBlock,
                                                           "parallel": ParallelBlock,
-                                                          "output_norm": OutputNormBlock}
+                                                          "output_norm": OutputNormBlock,
+                                                          "sandwich_norm": SandwichNormBlock}
 
 
 def register_arrangement(name: str, factory: Callable[[LayerSpec], Block], *, replace=False):
@@ -160,6 +202,7 @@ class CacheGroup:
     entries: tuple[int, ...]        # cache entry numbers, in pool order
     planes: int = 2                 # rows kept per token and head (keys and values: two)
     chunk: int = 0                  # > 0: only the rows of the chunk the request is in are kept
+    stride: int = 1                 # > 1: one row per block of this many positions
 
 
 class Model:
@@ -226,9 +269,22 @@ class Model:
         for gi, g in enumerate(self.cache_groups):
             for k, e in enumerate(g.entries):
                 self.entry_location[e] = (gi, k)
+        # entries that also keep one row per block of positions: companion groups at that rate
+        # (every position's block stays, so no window), behind the token groups
+        coarse: dict[tuple, list[int]] = {}
+        for entry in sorted(entry_req):
+            r = entry_req[entry]
+            if r.pool > 0:
+                coarse.setdefault((r.kv_heads, r.head_dim, r.planes, r.pool), []).append(entry)
+        self.coarse_location: dict[int, tuple[int, int]] = {}
+        for (kv_heads, head_dim, planes, pool), es in coarse.items():
+            gi = len(self.cache_groups)
+            self.cache_groups.append(CacheGroup(kv_heads, head_dim, 0, tuple(es), planes, 0, pool))
+            for k, e in enumerate(es):
+                self.coarse_location[e] = (gi, k)
 
     def kv_bytes_per_token(self, itemsize: int) -> int:
-        return sum(g.planes * g.kv_heads * g.head_dim * len(g.entries) * itemsize
+        return sum(-(-g.planes * g.kv_heads * g.head_dim * len(g.entries) * itemsize // g.stride)
                    for g in self.cache_groups)
 
     # -- weights --------------------------------------------------------------

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels.ops import ACTIVATIONS, AttentionGeometry
+from ..kernels.ops import ACTIVATIONS, LEARNED_ACTIVATIONS, AttentionGeometry
 from .base import (CacheRequest, Embedding, FeedForward, Head, Mixer, Norm, PositionEncoding,
                    TensorRequest, register_embedding, register_feed_forward, register_head,
                    register_mixer, register_norm, register_position)
@@ -73,18 +73,38 @@ class TokenEmbedding(Embedding):
 
 class LayerNorm(Norm):
     """y = (x - mean) / sqrt(var + eps) * weight + bias, statistics in float32
-    (heteroserve/model/numpy_engine.py:26-30)."""
+    (heteroserve/model/numpy_engine.py:26-30).  ``bias=None``: a norm with a weight alone.
 
-    def __init__(self, *, width: int, eps: float, weight: str, bias: str):
+    Besides ``forward`` it can be applied to a sublayer's OUTPUT and added into the stream in
+    one pass (``add_normed``), which an arrangement with norms behind its sublayers calls; the
+    same launch can form the rows the NEXT norm of the layer hands on (``then``)."""
+
+    def __init__(self, *, width: int, eps: float, weight: str, bias: str | None):
         self.width, self.eps, self.wn, self.bn = width, float(eps), weight, bias
         self.weight = self.bias = None
 
     def tensor_requests(self):
-        return {self.wn: TensorRequest((self.width,), "vector"),
-                self.bn: TensorRequest((self.width,), "vector")}
+        req = {self.wn: TensorRequest((self.width,), "vector")}
+        if self.bn:
+            req[self.bn] = TensorRequest((self.width,), "vector")
+        return req
 
     def bind(self, tensors):
-        self.weight, self.bias = tensors[self.wn], tensors[self.bn]
+        self.weight = tensors[self.wn]
+        self.bias = tensors[self.bn] if self.bn else torch.zeros_like(self.weight)
+
+    def add_normed(self, ctx, x, y, h=None, then=None):
+        """x += norm(y) for a float32 block ``y``.  With ``then=(norm, out)``, ``out`` also
+        receives ``norm(x)`` of the new rows (another layer norm's output, for the sublayer
+        that follows)."""
+        if then is not None and isinstance(then[0], LayerNorm):
+            nxt, out = then
+            ctx.ops.layernorm_add(x, y, self.weight, self.bias, self.eps, out=out,
+                                  out_gamma=nxt.weight, out_beta=nxt.bias, out_eps=nxt.eps)
+            return
+        ctx.ops.layernorm_add(x, y, self.weight, self.bias, self.eps)
+        if then is not None:
+            then[0].forward(ctx, then[1], x)
 
     def forward(self, ctx, out, x, rows=None):
         ctx.ops.layernorm(out, x, self.weight, self.bias, self.eps, rows)
@@ -183,10 +203,15 @@ class DenseFeedForward(FeedForward):
 
     def __init__(self, *, width: int, inner: int, activation: str, in_weight: str,
                  in_bias: str | None, out_weight: str, out_bias: str | None,
-                 stored_in_out: bool = True):
-        if activation not in ACTIVATIONS:
-            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ACTIVATIONS)}")
+                 stored_in_out: bool = True, act_params: str | None = None):
+        if activation not in ACTIVATIONS and activation not in LEARNED_ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: "
+                             f"{sorted(ACTIVATIONS) + sorted(LEARNED_ACTIVATIONS)}")
+        if (activation in LEARNED_ACTIVATIONS) != (act_params is not None):
+            raise ValueError(f"activation {activation!r}: act_params names the tensor of an "
+                             f"activation's learned numbers, and only of such a one")
         self.width, self.inner, self.act = width, inner, activation
+        self.act_name = act_params
         self.names = (in_weight, in_bias, out_weight, out_bias)
         self.stored_in_out = stored_in_out
         self.w_in = self.b_in = self.w_out = self.b_out = None
@@ -204,6 +229,8 @@ class DenseFeedForward(FeedForward):
             req[ib] = TensorRequest((self.inner,), "vector")
         if ob:
             req[ob] = TensorRequest((self.width,), "vector")
+        if self.act_name:
+            req[self.act_name] = TensorRequest((LEARNED_ACTIVATIONS[self.act],), "vector")
         return req
 
     def bind(self, tensors):
@@ -211,6 +238,9 @@ class DenseFeedForward(FeedForward):
         self.w_in, self.w_out = tensors[iw], tensors[ow]
         self.b_in = tensors[ib] if ib else None
         self.b_out = tensors[ob] if ob else None
+        # the learned numbers of the activation are read once and handed to the kernel by value
+        self.act_values = (tuple(float(v) for v in tensors[self.act_name].double().cpu())
+                           if self.act_name else ())
 
     takes_norm = True
     writes_fresh = True       # with fresh=True the result is written to x, not added into it
@@ -224,7 +254,16 @@ class DenseFeedForward(FeedForward):
     def forward(self, ctx, h, x, norm=None, fresh=False):
         T = h.shape[0]
         u = ctx.buffer("ff_inner", (T, self.inner), ctx.dtype)
-        if norm is not None:
+        if self.act_name:
+            # the product leaves float32 numbers; the activation reads them and writes the
+            # rows the second product takes
+            z = ctx.buffer("ff_inner_f32", (T, self.inner), torch.float32)
+            if norm is not None:
+                norm.linear(ctx, z, h, x, self.w_in, self.b_in)
+            else:
+                ctx.ops.linear(z, h, self.w_in, self.b_in)
+            ctx.ops.learned_act(u, z, self.act, self.act_values)
+        elif norm is not None:
             norm.linear(ctx, u, h, x, self.w_in, self.b_in, act=self.act)
         else:
             ctx.ops.linear(u, h, self.w_in, self.b_in, act=self.act)
@@ -273,9 +312,11 @@ class LinearHead(Head):
     """logits = h @ W^T in float32, W being [vocab, width]: the token table itself when the
     head is tied (heteroserve/model/weights.py:40-43, torch_engine.py:86-87)."""
 
-    def __init__(self, *, vocab_size: int, width: int, weight: str, scale: float = 1.0):
+    def __init__(self, *, vocab_size: int, width: int, weight: str, scale: float = 1.0,
+                 softcap: float = 0.0):
         self.vocab, self.width, self.name = vocab_size, width, weight
         self.scale = float(scale)          # logits = (h @ W^T) * scale
+        self.softcap = float(softcap)      # > 0: then logits = softcap * tanh(logits / softcap)
         self.weight = None
 
     def tensor_requests(self):
@@ -287,7 +328,8 @@ class LinearHead(Head):
     def forward(self, ctx, logits, h):
         # a step that samples and whose rows all take the argmax: the few-row kernel picks the
         # tokens while it streams the table (and stores the status word behind them)
-        fused = getattr(ctx.ops, "linear_argmax", None) if self.scale == 1.0 else None
+        plain = self.scale == 1.0 and self.softcap == 0.0
+        fused = getattr(ctx.ops, "linear_argmax", None) if plain else None
         if fused is not None and getattr(ctx, "sampling", False) \
                 and getattr(ctx, "greedy_only", False):
             tokens = ctx.buffer(getattr(ctx, "tokens_name", "sampled"), (logits.shape[0] + 1,), torch.int32)
@@ -296,11 +338,13 @@ class LinearHead(Head):
                 ctx.fused_tokens = tokens
                 return
         ctx.ops.linear(logits, h, self.weight)
-        if self.scale != 1.0:
+        if self.softcap > 0.0:
+            ctx.ops.scale_softcap_(logits, self.scale, self.softcap)
+        elif self.scale != 1.0:
             ctx.ops.scale_(logits, self.scale)
 
     def fused_decode_params(self):
-        if self.scale != 1.0:
+        if self.scale != 1.0 or self.softcap != 0.0:
             return None
         return dict(weight=self.weight, vocab=self.vocab, width=self.width)
 

@@ -447,3 +447,154 @@ class PlainOps:
                     S[hd] = decay[hd].to(self.cd) * S[hd] + torch.outer(k[hd], v[hd])
                     o[t, hd * vdim:(hd + 1) * vdim] = (S[hd].T @ q[hd]).to(o.dtype)
             state[slot] = S.reshape(-1).to(state.dtype)
+
+    # -- layer norm behind a sublayer, learned activation, capped logits ------------------
+    def _ln(self, v, gamma, beta, eps):
+        c = v - v.mean(-1, keepdim=True)
+        return c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * gamma.to(self.cd) \
+            + beta.to(self.cd)
+
+    def layernorm_add(self, x, y, gamma, beta, eps, out=None, out_gamma=None, out_beta=None,
+                      out_eps=None):
+        n = x.shape[0]
+        new = x.to(self.cd) + self._ln(y[:n].to(self.cd), gamma, beta, eps)
+        x.copy_(new.to(x.dtype))
+        if out is not None:
+            out.copy_(self._ln(x.to(self.cd), out_gamma, out_beta, out_eps).to(out.dtype))
+
+    def learned_act(self, out, z, act, values):
+        assert act == "xielu"
+        p, q = (torch.tensor(v, dtype=self.cd) for v in values)
+        sp = torch.nn.functional.softplus
+        v = z.to(self.cd)
+        pos = sp(p) * v * v + 0.5 * v
+        neg = (0.5 + sp(q)) * (torch.expm1(torch.clamp(v, max=0.0)) - v) + 0.5 * v
+        out.copy_(torch.where(v > 0, pos, neg).to(out.dtype))
+
+    def scale_softcap_(self, t, factor, cap):
+        t.copy_((cap * torch.tanh(t.to(self.cd) * factor / cap)).to(t.dtype))
+
+    # -- the real-gated linear recurrent unit ------------------------------------------------
+    def rglru_conv(self, u, proj, conv_w, conv_b, state, tok_req, req_start, req_slot, *, x_off,
+                   channels, taps):
+        C = channels
+        for t in range(u.shape[0]):
+            r = int(tok_req[t])
+            if r < 0:
+                continue
+            local, slot = t - int(req_start[r]), int(req_slot[r])
+            hist = state[slot, C:].view(taps - 1, C)            # oldest first
+            acc = conv_b.to(self.cd).clone()
+            for j in range(taps):
+                if local - j >= 0:
+                    src = proj[t - j, x_off:x_off + C]
+                else:
+                    src = hist[taps - 1 + (local - j)]
+                acc = acc + conv_w[:, taps - 1 - j].to(self.cd) * src.to(self.cd)
+            u[t] = acc.to(u.dtype)
+
+    def rglru_scan(self, out, state, u, z, proj, b_gates, rate, req_start, req_len, req_slot, *,
+                   channels, blocks, taps, decay_scale, y_off, x_off):
+        C, n = channels, channels // blocks
+        for r in range(req_start.shape[0]):
+            cnt = int(req_len[r])
+            if cnt <= 0:
+                continue
+            t0, slot = int(req_start[r]), int(req_slot[r])
+            S = state[slot, :C].to(self.cd)
+            for t in range(t0, t0 + cnt):
+                zz = (z[t].to(self.cd) + b_gates.to(self.cd)).view(blocks, 2, n)
+                rg = torch.sigmoid(zz[:, 0]).reshape(C)
+                ig = torch.sigmoid(zz[:, 1]).reshape(C)
+                log_a = -decay_scale * rg * rate.to(self.cd)
+                a = torch.exp(log_a)
+                S = a * S + torch.sqrt(-torch.expm1(2.0 * log_a)) * ig * u[t].to(self.cd)
+                y = _ACT["gelu_tanh"](proj[t, y_off:y_off + C].to(self.cd))
+                out[t] = (S * y).to(out.dtype)
+            state[slot, :C] = S.to(state.dtype)
+            if taps > 1:
+                old = state[slot, C:].view(taps - 1, C)
+                rows = torch.cat([old, proj[t0:t0 + cnt, x_off:x_off + C].to(state.dtype)])
+                state[slot, C:] = rows[-(taps - 1):].reshape(-1)
+
+    # -- attention over a window and pooled blocks ---------------------------------------------
+    def _turn_halves(self, vec, position, freq, dims, sign=1.0):
+        out = vec.to(self.cd).clone()
+        if freq is None or not dims:
+            return out
+        half = dims // 2
+        ang = sign * float(position) * freq[:half].to(self.cd)
+        c, s = torch.cos(ang), torch.sin(ang)
+        lo, hi = out[..., :half].clone(), out[..., half:dims].clone()
+        out[..., :half] = lo * c - hi * s
+        out[..., half:dims] = hi * c + lo * s
+        return out
+
+    def pooled_prepare(self, q_out, pool, proj, wq, wk, freq_qk, freq_v, table, tok_pos, tok_req,
+                       *, n_heads, n_kv_heads, head_dim, value_dim, rot_dims, eps, writes,
+                       page_size, status):
+        H, G, D, V = n_heads, n_kv_heads, head_dim, value_dim
+        rows = pool.view(-1, G, page_size, D + V)
+        for t in range(q_out.shape[0]):
+            r = int(tok_req[t])
+            if r < 0:
+                continue
+            p = int(tok_pos[t])
+            row = proj[t].to(self.cd)
+            q = row[:H * D].view(H, D)
+            k = row[H * D:(H + G) * D].view(G, D)
+            v = row[(H + G) * D:(H + G) * D + G * V].view(G, V)
+            if wq is not None:
+                q = self._rms(q, eps) * wq.to(self.cd)
+            if wk is not None:
+                k = self._rms(k, eps) * wk.to(self.cd)
+            q_out[t] = self._turn_halves(q, p, freq_qk, rot_dims).reshape(-1).to(q_out.dtype)
+            if not writes:
+                continue
+            k = self._turn_halves(k, p, freq_qk, rot_dims)
+            v = self._turn_halves(v, p, freq_v, V if freq_v is not None else 0)
+            page = int(table[r, p // page_size])
+            rows[page, :, p % page_size] = torch.cat([k, v], dim=1).to(pool.dtype)
+
+    def pooled_means(self, coarse_pool, coarse_table, pool, table, tok_pos, tok_req, *,
+                     n_kv_heads, row, block, page_size, status):
+        src = pool.view(-1, n_kv_heads, page_size, row)
+        dst = coarse_pool.view(-1, n_kv_heads, page_size, row)
+        for t in range(tok_pos.shape[0]):
+            r, p = int(tok_req[t]), int(tok_pos[t])
+            if r < 0 or (p + 1) % block:
+                continue
+            b = p // block
+            acc = torch.zeros(n_kv_heads, row, dtype=self.cd)
+            for j in range(b * block, p + 1):
+                acc += src[int(table[r, j // page_size]), :, j % page_size].to(self.cd)
+            dst[int(coarse_table[r, b // page_size]), :, b % page_size] = \
+                (acc / block).to(coarse_pool.dtype)
+
+    def pooled_attention(self, out, q, pool, table, coarse_pool, coarse_table, tok_pos, tok_req,
+                         freq_v, *, n_heads, n_kv_heads, head_dim, value_dim, window, block,
+                         scale, page_size, status):
+        H, G, D, V = n_heads, n_kv_heads, head_dim, value_dim
+        fine = pool.view(-1, G, page_size, D + V)
+        coarse = coarse_pool.view(-1, G, page_size, D + V)
+        for t in range(out.shape[0]):
+            r = int(tok_req[t])
+            if r < 0:
+                continue
+            i = int(tok_pos[t])
+            seen = max(0, (i - window + 1) // block)
+            first = max(0, i - window + 1)
+            o = torch.zeros(H, V, dtype=self.cd)
+            for g in range(G):
+                rows = [coarse[int(coarse_table[r, b // page_size]), g, b % page_size]
+                        for b in range(seen)]
+                rows += [fine[int(table[r, j // page_size]), g, j % page_size]
+                         for j in range(first, i + 1)]
+                kv = torch.stack(rows).to(self.cd)
+                for h in range(g * (H // G), (g + 1) * (H // G)):
+                    qv = q[t, h * D:(h + 1) * D].to(self.cd)
+                    w = torch.softmax((kv[:, :D] @ qv) * scale, 0)
+                    o[h] = w @ kv[:, D:]
+            if freq_v is not None:
+                o = self._turn_halves(o, i, freq_v, V, sign=-1.0)
+            out[t] = o.reshape(-1).to(out.dtype)
