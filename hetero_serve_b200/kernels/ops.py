@@ -13,6 +13,7 @@ signature; the kernel tests compare the two.
 from __future__ import annotations
 
 import ctypes
+import math
 from ctypes import c_float, c_int, c_void_p
 from dataclasses import dataclass
 
@@ -212,6 +213,16 @@ def _declare(lib) -> None:
         "hs_biased_attention_prefill": [P, P, P, P, P, P, I, P, P, I, P, I, I, I, I, I, I, I, I,
                                         F, F, I, I, P, P],
         "hs_lightning_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
+        "hs_layernorm_add": [P, P, P, P, F, P, P, P, F, I, I, I, P],
+        "hs_learned_act_xielu": [P, P, ctypes.c_longlong, F, F, I, P],
+        "hs_scale_softcap": [P, ctypes.c_longlong, F, F, P],
+        "hs_rglru_conv": [P, P, I, I, P, P, P, I, P, P, P, I, I, I, P],
+        "hs_rglru_scan": [P, P, I, P, P, P, I, I, I, P, P, P, P, P, I, I, I, I, F, I, P],
+        "hs_pooled_prepare": [P, P, P, I, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, I,
+                              I, P, P],
+        "hs_pooled_means": [P, P, I, I, P, P, I, I, P, P, I, I, I, I, I, I, P, P],
+        "hs_pooled_attention": [P, P, P, P, I, I, P, P, I, I, P, P, P, I, I, I, I, I, I, I, F, I,
+                                I, I, P, P],
         "hs_moe_sorted_scratch": [I, I, I, I, I, I, P, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P, P],
     }
@@ -1490,6 +1501,170 @@ class CudaOps:
             _ptr(req_slot), req_start.shape[0], T, proj.shape[1], int(q_off), int(k_off),
             int(v_off), heads, dim, vdim, ACTIVATIONS[act], _ptr(scratch), self._stream()),
             f"lightning_recurrence(dim={dim},vdim={vdim})")
+
+    # -- norms behind a sublayer, a learned activation, capped logits -----------------------
+    def layernorm_add(self, x, y, gamma, beta, eps, out=None, out_gamma=None, out_beta=None,
+                      out_eps=None):
+        """x += LayerNorm(y) * gamma + beta for the float32 rows of ``y`` (``beta`` may be
+        None); with ``out``, also out = LayerNorm(new x) * out_gamma + out_beta: the rows the
+        next sublayer takes, in the compute type."""
+        _want(x, "x", torch.float32, 2)
+        _want(y, "y", torch.float32, 2)
+        _want(gamma, "gamma", torch.float32, 1)
+        n, width = x.shape
+        if y.shape[0] < n or y.shape[1] != width or gamma.shape[0] != width:
+            raise KernelError("layernorm_add: shapes do not fit")
+        for name, v in (("beta", beta), ("out_gamma", out_gamma), ("out_beta", out_beta)):
+            if v is not None:
+                _want(v, name, torch.float32, 1)
+                if v.shape[0] != width:
+                    raise KernelError(f"layernorm_add: {name} has another width")
+        if out is not None:
+            _want(out, "out", _FLOATS, 2)
+            if tuple(out.shape) != (n, width) or out_gamma is None:
+                raise KernelError("layernorm_add: out needs x's shape and a weight")
+        self.launches += 1
+        _check(self.lib.hs_layernorm_add(
+            _ptr(x), _ptr(y), _ptr(gamma), _ptr(beta), float(eps), _ptr(out), _ptr(out_gamma),
+            _ptr(out_beta), float(eps if out_eps is None else out_eps), n, width,
+            _DT[out.dtype] if out is not None else 0, self._stream()),
+            f"layernorm_add(width={width})")
+
+    def learned_act(self, out, z, act, values):
+        """out = act(z) for an activation with learned numbers ``values``; z float32.
+        xielu, values (p, q): z > 0: softplus(p) z^2 + z/2; else (1/2 + softplus(q))
+        (e^z - 1 - z) + z/2."""
+        if act != "xielu" or len(values) != LEARNED_ACTIVATIONS["xielu"]:
+            raise KernelError(f"learned_act: activation {act!r} with {len(values)} numbers not taken")
+        _want(out, "out", _FLOATS)
+        _want(z, "z", torch.float32)
+        if out.numel() != z.numel():
+            raise KernelError("learned_act: sizes differ")
+        sp = lambda v: math.log1p(math.exp(-abs(v))) + max(v, 0.0)      # softplus, in double
+        self.launches += 1
+        _check(self.lib.hs_learned_act_xielu(_ptr(out), _ptr(z), z.numel(), sp(values[0]),
+                                             0.5 + sp(values[1]), _DT[out.dtype], self._stream()),
+               "learned_act")
+
+    def scale_softcap_(self, t, factor, cap):
+        """t = cap * tanh(t * factor / cap), in place (float32)."""
+        _want(t, "t", torch.float32)
+        self.launches += 1
+        _check(self.lib.hs_scale_softcap(_ptr(t), t.numel(), float(factor), float(cap),
+                                         self._stream()), "scale_softcap")
+
+    # -- the real-gated linear recurrent unit -----------------------------------------------
+    def rglru_conv(self, u, proj, conv_w, conv_b, state, tok_req, req_start, req_slot, *, x_off,
+                   channels, taps):
+        """u[t, c] = conv_b[c] + sum_j conv_w[c, taps-1-j] * x[t-j, c], x = the columns
+        ``x_off .. x_off + channels`` of the float32 rows ``proj``; rows before a request's
+        first token of this step come from its slot of ``state`` ([slots, channels * taps]:
+        the recurrence's state, then the last taps-1 inputs, oldest first)."""
+        for name, v in (("u", u), ("proj", proj), ("conv_w", conv_w)):
+            _want(v, name, torch.float32, 2)
+        _want(conv_b, "conv_b", torch.float32, 1)
+        _want(state, "state", torch.float32, 2)
+        C, T = int(channels), u.shape[0]
+        if u.shape[1] != C or tuple(conv_w.shape) != (C, taps) or conv_b.shape[0] != C \
+                or x_off + C > proj.shape[1] or proj.shape[0] < T or state.shape[1] < C * taps:
+            raise KernelError("rglru_conv: shapes do not fit")
+        self.launches += 1
+        _check(self.lib.hs_rglru_conv(_ptr(u), _ptr(proj), proj.shape[1], int(x_off),
+                                      _ptr(conv_w), _ptr(conv_b), _ptr(state), state.shape[1],
+                                      _ptr(tok_req), _ptr(req_start), _ptr(req_slot), T, C,
+                                      int(taps), self._stream()), f"rglru_conv(channels={C})")
+
+    def rglru_scan(self, out, state, u, z, proj, b_gates, rate, req_start, req_len, req_slot, *,
+                   channels, blocks, taps, decay_scale, y_off, x_off):
+        """Per request and channel, over the tokens of this step, on the float32 state of the
+        request's slot: r, i = sigmoid(z + b_gates) (columns [part][r | i][channels/blocks]),
+        log a = -decay_scale * r * rate, S <- a S + sqrt(1 - a^2) i u, out = S * gelu_tanh(y);
+        then the state and the convolution's last inputs are stored."""
+        for name, v in (("u", u), ("z", z), ("proj", proj), ("state", state)):
+            _want(v, name, torch.float32, 2)
+        _want(out, "out", _FLOATS, 2)
+        _want(b_gates, "b_gates", torch.float32, 1)
+        _want(rate, "rate", torch.float32, 1)
+        C = int(channels)
+        if out.shape[1] != C or u.shape[1] != C or z.shape[1] != 2 * C or rate.shape[0] != C \
+                or b_gates.shape[0] != 2 * C or state.shape[1] < C * taps \
+                or max(y_off, x_off) + C > proj.shape[1]:
+            raise KernelError("rglru_scan: shapes do not fit")
+        self.launches += 1
+        _check(self.lib.hs_rglru_scan(
+            _ptr(out), _ptr(state), state.shape[1], _ptr(u), _ptr(z), _ptr(proj), proj.shape[1],
+            int(y_off), int(x_off), _ptr(b_gates), _ptr(rate), _ptr(req_start), _ptr(req_len),
+            _ptr(req_slot), req_start.shape[0], C, int(blocks), int(taps), float(decay_scale),
+            _DT[out.dtype], self._stream()), f"rglru_scan(channels={C})")
+
+    # -- attention over a window and pooled blocks --------------------------------------------
+    def pooled_prepare(self, q_out, pool, proj, wq, wk, freq_qk, freq_v, table, tok_pos, tok_req,
+                       *, n_heads, n_kv_heads, head_dim, value_dim, rot_dims, eps, writes,
+                       page_size, status):
+        """From the float32 rows [q | k | v] of ``proj``: per-head RMS norms of q and k
+        (weights ``wq``, ``wk`` or None), rotation of their first ``rot_dims`` numbers by the
+        position (pairs d, d + rot_dims/2), rotation of the values over all of value_dim
+        (``freq_v`` or None); q to ``q_out`` (float32), and with ``writes`` the row [k | v] of
+        every key/value head into the token's page."""
+        _want(q_out, "q_out", torch.float32, 2)
+        _want(proj, "proj", torch.float32, 2)
+        _want(pool, "pool", _FLOATS)
+        _want(table, "table", torch.int32, 2)
+        H, G, D, V = n_heads, n_kv_heads, head_dim, value_dim
+        if q_out.shape[1] != H * D or proj.shape[1] < (H + G) * D + G * V:
+            raise KernelError("pooled_prepare: the rows do not fit the heads")
+        num_pages = pool.numel() // (G * page_size * (D + V))
+        self.launches += 1
+        _check(self.lib.hs_pooled_prepare(
+            _ptr(q_out), _ptr(pool), _ptr(proj), proj.shape[1], _ptr(wq), _ptr(wk),
+            _ptr(freq_qk), _ptr(freq_v), _ptr(table), table.shape[1], num_pages, _ptr(tok_pos),
+            _ptr(tok_req), q_out.shape[0], H, G, D, V, int(rot_dims), float(eps), int(page_size),
+            int(bool(writes)), _DT[pool.dtype], _ptr(status), self._stream()),
+            f"pooled_prepare(head_dim={D},value_dim={V})")
+
+    def pooled_means(self, coarse_pool, coarse_table, pool, table, tok_pos, tok_req, *,
+                     n_kv_heads, row, block, page_size, status):
+        """For every token whose position completes a block of ``block`` positions: the mean of
+        the block's rows as ``pool`` holds them, written as row ``position // block`` of the
+        companion pool."""
+        _want(coarse_pool, "coarse_pool", pool.dtype)
+        _want(pool, "pool", _FLOATS)
+        _want(table, "table", torch.int32, 2)
+        _want(coarse_table, "coarse_table", torch.int32, 2)
+        per_page = n_kv_heads * page_size * row
+        self.launches += 1
+        _check(self.lib.hs_pooled_means(
+            _ptr(coarse_pool), _ptr(coarse_table), coarse_table.shape[1],
+            coarse_pool.numel() // per_page, _ptr(pool), _ptr(table), table.shape[1],
+            pool.numel() // per_page, _ptr(tok_pos), _ptr(tok_req), tok_pos.shape[0],
+            int(n_kv_heads), int(row), int(block), int(page_size), _DT[pool.dtype], _ptr(status),
+            self._stream()), f"pooled_means(block={block})")
+
+    def pooled_attention(self, out, q, pool, table, coarse_pool, coarse_table, tok_pos, tok_req,
+                         freq_v, *, n_heads, n_kv_heads, head_dim, value_dim, window, block,
+                         scale, page_size, status):
+        """Per token at position i and query head: one softmax over the mean rows of the blocks
+        b with b * block + block - 1 <= i - window and the token rows j with 0 <= i - j <
+        window; the output turned back by -i over value_dim (``freq_v`` or None)."""
+        _want(out, "out", _FLOATS, 2)
+        _want(q, "q", torch.float32, 2)
+        _want(pool, "pool", _FLOATS)
+        _want(coarse_pool, "coarse_pool", pool.dtype)
+        H, G, D, V = n_heads, n_kv_heads, head_dim, value_dim
+        T = out.shape[0]
+        if out.shape[1] != H * V or q.shape[1] != H * D or q.shape[0] < T:
+            raise KernelError("pooled_attention: the rows do not fit the heads")
+        if out.dtype != pool.dtype:
+            raise KernelError("pooled_attention: out has the cache's type")
+        per_page = G * page_size * (D + V)
+        self.launches += 1
+        _check(self.lib.hs_pooled_attention(
+            _ptr(out), _ptr(q), _ptr(pool), _ptr(table), table.shape[1], pool.numel() // per_page,
+            _ptr(coarse_pool), _ptr(coarse_table), coarse_table.shape[1],
+            coarse_pool.numel() // per_page, _ptr(tok_pos), _ptr(tok_req), _ptr(freq_v), T, H, G,
+            D, V, int(window), int(block), float(scale), int(page_size), _DT[pool.dtype],
+            _DT[out.dtype], _ptr(status), self._stream()),
+            f"pooled_attention(head_dim={D},value_dim={V})")
 
     # -- sampling ---------------------------------------------------------------
     def argmax(self, out, logits):

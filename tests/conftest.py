@@ -117,3 +117,14 @@ def putelix_cases(tmp_path_factory):
 @pytest.fixture(params=["case_a", "case_b", "case_d"])
 def putelix_case(request, putelix_cases):
     return putelix_cases[request.param]
+
+
+@pytest.fixture(scope="session")
+def roritar_cases(tmp_path_factory):
+    import roritar_cases as rc
+    return rc.make_cases(tmp_path_factory)
+
+
+@pytest.fixture(params=["case_a", "case_b"])
+def roritar_case(request, roritar_cases):
+    return roritar_cases[request.param]
