@@ -179,9 +179,8 @@ __device__ __forceinline__ float dot_row(const __nv_bfloat16* __restrict__ k, co
   return s;
 }
 
-constexpr int PA_MAXC = 8;       // value columns a lane owns at most (V <= 256)
-
-template <typename TC, typename TO>
+// PA_MAXC: value columns a lane owns (V <= 32 * PA_MAXC); the launcher picks 2, 8 or 32
+template <typename TC, typename TO, int PA_MAXC>
 __global__ void __launch_bounds__(PA_WARPS * 32)
 pooled_attention_kernel(TO* __restrict__ out, const float* __restrict__ q,
                         const TC* __restrict__ pool, const int* __restrict__ table,
@@ -355,7 +354,7 @@ HS_EXPORT int hs_pooled_attention(void* out, const float* q, const void* pool, c
                                   int* status, void* stream) {
   if (!out || !q || !pool || !table || !coarse || !ctable || !tok_pos || !tok_req || !status)
     return HS_ERR_ARGUMENT;
-  if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0 || V > 32 * hs::PA_MAXC || window <= 0 ||
+  if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0 || V > 1024 || window <= 0 ||
       block <= 0 || page_size <= 0 || (freq_v && V % 2))
     return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
@@ -369,14 +368,21 @@ HS_EXPORT int hs_pooled_attention(void* out, const float* q, const void* pool, c
   const int per16 = cache_dtype == HS_DT_BF16 ? 8 : 4;
   const int vec = (D % per16 == 0 && V % per16 == 0) ? 1 : 0;
   cudaError_t e;
-#define HS_PA_LAUNCH(TC, TO)                                                                     \
-  e = hs_launch(hs::pooled_attention_kernel<TC, TO>, grid, blk, smem, st, pdl, (TO*)out, q,      \
+#define HS_PA_LAUNCH_C(TC, TO, C)                                                                \
+  e = hs_launch(hs::pooled_attention_kernel<TC, TO, C>, grid, blk, smem, st, pdl, (TO*)out, q,   \
                 (const TC*)pool, table, max_pages, num_pages, (const TC*)coarse, ctable,         \
                 cmax_pages, cnum_pages, tok_pos, tok_req, freq_v, n_tokens, H, G, D, V, window,  \
                 block, scale, page_size, vec, status)
+#define HS_PA_LAUNCH(TC, TO)                                                                     \
+  do {                                                                                           \
+    if (V <= 64) HS_PA_LAUNCH_C(TC, TO, 2);                                                      \
+    else if (V <= 256) HS_PA_LAUNCH_C(TC, TO, 8);                                                \
+    else HS_PA_LAUNCH_C(TC, TO, 32);                                                             \
+  } while (0)
   if (cache_dtype == HS_DT_BF16 && out_dtype == HS_DT_BF16) HS_PA_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (cache_dtype == HS_DT_F32 && out_dtype == HS_DT_F32) HS_PA_LAUNCH(float, float);
   else return HS_ERR_UNSUPPORTED;
 #undef HS_PA_LAUNCH
+#undef HS_PA_LAUNCH_C
   return e == cudaSuccess ? HS_OK : (int)e;
 }

@@ -272,9 +272,15 @@ class Runner:
             self.ops.fused_decode_on = True
             self.fused = plan_fused_decode(model, self.ops, self.storage, page_size)
         self.workspace = Workspace(self.device)
-        # an architecture without a limit of its own can hold what the pool can
-        self.max_positions = model.spec.max_positions or min(num_pages * page_size,
-                                                             UNBOUNDED_MODEL_POSITIONS)
+        # an architecture without a limit of its own can hold what its groups can: a group that
+        # keeps every position (or every block of positions) holds its pool's worth, a group
+        # that keeps a window or a chunk gives its pages back and sets no limit
+        holds = [pool.num_pages * page_size * g.stride
+                 for g, pool in zip(self.manager.groups, self.manager.pools)
+                 if g.window == 0 and g.chunk == 0]
+        self.max_positions = model.spec.max_positions or min(
+            holds + [UNBOUNDED_MODEL_POSITIONS] if model.cache_groups
+            else [num_pages * page_size, UNBOUNDED_MODEL_POSITIONS])
         self.max_pages = [max(1, self.manager.pages_for(self.max_positions, gi))
                           for gi in range(len(model.cache_groups))]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)

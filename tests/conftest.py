@@ -128,3 +128,9 @@ def roritar_cases(tmp_path_factory):
 @pytest.fixture(params=["case_a", "case_b"])
 def roritar_case(request, roritar_cases):
     return roritar_cases[request.param]
+
+
+@pytest.fixture(scope="session")
+def roritar_planted(tmp_path_factory):
+    import roritar_cases as rc
+    return rc.planted_case(tmp_path_factory)

@@ -96,6 +96,53 @@ def make_cases(tmp_path_factory):
     return out
 
 
+# -- a model in which ONE key stands out ------------------------------------------------------
+# Token ASK's query and token MARK's key meet in one unrotated number of each head and nowhere
+# else: every other pair of tokens scores 0 there, so an ASK query gives nearly all of its softmax
+# to an earlier MARK it can see (or to the block mean that holds it), and an edge that is one position
+# off changes the logits by far more than any tolerance.  The model is this one layer, so a MARK
+# that is not visible changes nothing at all.
+MARK, ASK = 7, 11
+PLANTED = _model(97, 32, 1e-5, [
+    _layer("attention", _att(2, 1, 16, 8, 13, 4, 8, base=100.0, scale=1.0), 40),
+], logit_scale=1.0, softcap=20.0)
+
+
+def planted_case(tmp_path_factory, strength=14.0):
+    from hetero_serve_b200.config.model_config import architecture_of
+    from hetero_serve_b200.weights import write_safetensors
+    arch = architecture_of(PLANTED)
+    cfg = arch.config_cls.from_dict(PLANTED)
+    w = arch.init_weights(cfg, 41)
+    m = PLANTED["layers"][0]["mixer"]
+    D, W = m["dim"], PLANTED["width"]
+    w["embed"][:, :4] = 0.0
+    w["embed"][MARK, 0], w["embed"][MARK, 1] = 3.0, -3.0
+    w["embed"][ASK, 2], w["embed"][ASK, 3] = 3.0, -3.0
+    w["l0.norm1"] = torch.ones(W)
+    probe = torch.zeros(2, W)                       # rows that sum to 0: the norm's mean drops out
+    probe[0, 0], probe[0, 1] = 1.0, -1.0
+    probe[1, 2], probe[1, 3] = 1.0, -1.0
+    for hd in range(m["heads"]):
+        w["l0.mix.q"][hd * D + D - 1] = probe[1]
+    w["l0.mix.k"][D - 1] = probe[0]
+    w["l0.mix.q.norm"] = torch.zeros(D)
+    w["l0.mix.q.norm"][D - 1] = strength
+    w["l0.mix.k.norm"] = torch.ones(D)
+    folder = tmp_path_factory.mktemp("roritar_planted")
+    (folder / "config.json").write_text(json.dumps(cfg.to_dict(), indent=2) + "\n")
+    write_safetensors(folder / "model.safetensors", w, {"format": "pt"})
+    return Case("planted", folder, json.loads((folder / "config.json").read_text()), 41)
+
+
+def planted_tokens(case, mark_at, length, seed):
+    """Random tokens without MARK and ASK, then MARK at ``mark_at`` and ASK as the last token."""
+    t = [x if x not in (MARK, ASK) else MARK + 1 for x in case.tokens(length, seed)]
+    t[mark_at] = MARK
+    t[-1] = ASK
+    return t
+
+
 def rms_error(got, want):
     """Root mean square of the difference with its mean taken off, over the root mean square
     of the wanted row."""

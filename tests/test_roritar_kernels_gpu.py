@@ -1,0 +1,258 @@
+"""The kernels of the Roritar parts, each mechanism alone, against the plain implementation's
+function of the same mechanism (tests/plain_roritar.py, float64 on the CPU): layer norms
+behind a sublayer, the learned activation, capped logits, the real-gated recurrence with its
+short convolution and block-diagonal gates, and attention over a window and pooled blocks
+over a paged cache whose pages are in no order."""
+
+import math
+
+import pytest
+import torch
+
+import plain_roritar as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+F32, BF16, I32, F64 = torch.float32, torch.bfloat16, torch.int32, torch.float64
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from hetero_serve_b200.kernels import CudaOps
+    return CudaOps(DEV)
+
+
+def rnd(*shape, seed=0, std=1.0, dtype=F32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+
+def dev(*ts):
+    out = tuple(t.to(DEV).contiguous() for t in ts)
+    return out if len(out) > 1 else out[0]
+
+
+def ints(v):
+    return torch.tensor(list(v), dtype=I32, device=DEV)
+
+
+def close(got, want, tol):
+    want = want.double()
+    err = ((got.detach().cpu().double() - want).abs() / (1.0 + want.abs())).max().item()
+    assert err <= tol, err
+
+
+# -- norms, activation, cap ----------------------------------------------------------------------
+@pytest.mark.parametrize("dtype, tol", [(F32, 1e-4), (BF16, 2e-2)])
+@pytest.mark.parametrize("width", [1, 5, 100, 1030, 5000])
+def test_layernorm_add(ops, dtype, tol, width):
+    """A large eps so that it shows; rows whose mean is a hundred times their spread, where a
+    variance formed as E[y^2] - E[y]^2 would be off by ten times the tolerance."""
+    x, y = rnd(7, width, seed=1), rnd(9, width, seed=2, std=0.3) + 30.0
+    g, g2 = rnd(width, seed=3) + 1.0, rnd(width, seed=4) + 1.0
+    want = x.double() + P.layer_norm(y[:7].double(), g.double(), 1e-3)
+    want2 = P.layer_norm(want, g2.double(), 2e-2)
+    got = dev(x.clone())
+    ops.layernorm_add(got, dev(y), dev(g), None, 1e-3)
+    close(got, want, 1e-4)
+    got, out = dev(x.clone()), torch.zeros(7, width, dtype=dtype, device=DEV)
+    ops.layernorm_add(got, dev(y), dev(g), None, 1e-3, out=out, out_gamma=dev(g2), out_eps=2e-2)
+    close(got, want, 1e-4)
+    close(out, want2, tol)
+
+
+@pytest.mark.parametrize("dtype, tol", [(F32, 2e-6), (BF16, 8e-3)])
+def test_learned_activation(ops, dtype, tol):
+    z = torch.cat([rnd(3, 333, seed=5, std=3.0), torch.tensor([[0.0, -0.0, 1e-8, -1e-8, -30.0, 30.0]
+                                                                + [0.5] * 327])])
+    for p, q in ((0.3, -0.2), (-4.0, 2.5), (0.0, 0.0)):
+        want = P.xielu(z.double(), torch.tensor(p, dtype=F64), torch.tensor(q, dtype=F64))
+        out = torch.zeros(4, 333, dtype=dtype, device=DEV)
+        ops.learned_act(out, dev(z), "xielu", (p, q))
+        close(out, want, tol)
+
+
+def test_scaled_and_capped_logits(ops):
+    z = rnd(5, 777, seed=6, std=40.0)
+    for s, cap in ((0.25, 15.0), (1.0, 30.0), (3.0, 0.5)):
+        got = dev(z.clone())
+        ops.scale_softcap_(got, s, cap)
+        close(got, cap * torch.tanh(z.double() * s / cap), 2e-6)
+
+
+# -- the recurrence -------------------------------------------------------------------------------
+def _recurrence_weights(C, B, taps, seed):
+    n = C // B
+    w = {"m.conv": rnd(C, taps, seed=seed, std=0.5), "m.conv.b": rnd(C, seed=seed + 1, std=0.2),
+         "m.ra": rnd(B, n, n, seed=seed + 2, std=1 / math.sqrt(n)), "m.ra.b": rnd(B, n, seed=seed + 3),
+         "m.ri": rnd(B, n, n, seed=seed + 4, std=1 / math.sqrt(n)), "m.ri.b": rnd(B, n, seed=seed + 5),
+         "m.lam": rnd(C, seed=seed + 6) - 2.0}
+    # the oracle's projections pick the two halves of a row [y | x] apart
+    eye = torch.eye(C)
+    w["m.y"], w["m.x"] = torch.cat([eye, 0 * eye], 1), torch.cat([0 * eye, eye], 1)
+    w["m.y.b"] = w["m.x.b"] = torch.zeros(C)
+    w["m.o"] = eye
+    return w
+
+
+@pytest.mark.parametrize("dtype, tol", [(F32, 5e-6), (BF16, 1e-2)])
+@pytest.mark.parametrize("C, B, taps", [(40, 2, 4), (36, 3, 3), (24, 1, 1), (256, 4, 4), (70, 7, 2)])
+def test_recurrence_in_portions_and_batches(ops, dtype, tol, C, B, taps):
+    """Three requests side by side in slots that are in no order, cut into portions of unequal
+    length (one shorter than the convolution's history, one long enough to be scanned in
+    segments), one of them in a slot that another request left."""
+    w = _recurrence_weights(C, B, taps, 10)
+    w64 = {k: v.double() for k, v in w.items()}
+    n = C // B
+    w_gates = dev(torch.cat([w["m.ra"].transpose(1, 2), w["m.ri"].transpose(1, 2)], 2))
+    b_gates = dev(torch.cat([w["m.ra.b"], w["m.ri.b"]], 1).reshape(-1))
+    rate = dev(torch.nn.functional.softplus(w["m.lam"].double()).float())
+    cw, cb = dev(w["m.conv"]), dev(w["m.conv.b"])
+    rows = {"a": rnd(331, 2 * C, seed=20), "b": rnd(12, 2 * C, seed=21), "c": rnd(60, 2 * C, seed=22)}
+    want = {r: P.rglru(h.double(), w64, "m.", {"blocks": B}) for r, h in rows.items()}
+    slots = {"a": 3, "b": 0, "c": 2}
+    state = torch.full((4, C * taps), 7.0, device=DEV)          # what a former owner left
+    plan = [[("a", 2), ("b", 1)], [("a", 1), ("b", 5), ("c", 9)], [("a", 300), ("c", 1)],
+            [("c", 50), ("b", 6), ("a", 28)]]
+    fed = {r: 0 for r in rows}
+    for step in plan:
+        for r, _ in step:
+            if fed[r] == 0:
+                state[slots[r]] = 0.0                            # a slot is cleared when taken
+        proj = torch.cat([rows[r][fed[r]:fed[r] + k] for r, k in step])
+        T = proj.shape[0]
+        starts, at = [], 0
+        for r, k in step:
+            starts.append(at)
+            at += k
+        tok_req = ints(i for i, (_, k) in enumerate(step) for _ in range(k))
+        req_start, req_len = ints(starts), ints(k for _, k in step)
+        req_slot = ints(slots[r] for r, _ in step)
+        proj = dev(proj)
+        u = torch.zeros(T, C, device=DEV)
+        ops.rglru_conv(u, proj, cw, cb, state, tok_req, req_start, req_slot, x_off=C,
+                       channels=C, taps=taps)
+        z = torch.zeros(T, 2 * C, device=DEV)
+        ops.grouped_linear(z, u, w_gates)
+        out = torch.zeros(T, C, dtype=dtype, device=DEV)
+        ops.rglru_scan(out, state, u, z, proj, b_gates, rate, req_start, req_len, req_slot,
+                       channels=C, blocks=B, taps=taps, decay_scale=8.0, y_off=0, x_off=C)
+        for (r, k), s in zip(step, starts):
+            close(out[s:s + k], want[r][fed[r]:fed[r] + k], tol)
+            fed[r] += k
+    assert fed == {r: h.shape[0] for r, h in rows.items()}
+
+
+def test_recurrence_keeps_a_long_memory(ops):
+    """A decay close to 1: sqrt(1 - a^2) must keep its digits, and the state of the first token
+    still counts after hundreds of steps taken one at a time."""
+    C, B, taps = 8, 1, 2
+    w = _recurrence_weights(C, B, taps, 30)
+    w["m.lam"] = torch.full((C,), -9.0)                        # a = exp(-8 r softplus(-9)): 0.999..
+    w64 = {k: v.double() for k, v in w.items()}
+    h = rnd(400, 2 * C, seed=31)
+    h[0, C:] += 50.0                                           # a large first input
+    want = P.rglru(h.double(), w64, "m.", {"blocks": B})
+    w_gates = dev(torch.cat([w["m.ra"].transpose(1, 2), w["m.ri"].transpose(1, 2)], 2))
+    b_gates = dev(torch.cat([w["m.ra.b"], w["m.ri.b"]], 1).reshape(-1))
+    rate = dev(torch.nn.functional.softplus(w["m.lam"].double()).float())
+    state = torch.zeros(1, C * taps, device=DEV)
+    one, zero = ints([1]), ints([0])
+    for t in range(400):
+        proj = dev(h[t:t + 1])
+        u, z = torch.zeros(1, C, device=DEV), torch.zeros(1, 2 * C, device=DEV)
+        ops.rglru_conv(u, proj, dev(w["m.conv"]), dev(w["m.conv.b"]), state, zero, zero, zero,
+                       x_off=C, channels=C, taps=taps)
+        ops.grouped_linear(z, u, w_gates)
+        out = torch.zeros(1, C, device=DEV)
+        ops.rglru_scan(out, state, u, z, proj, b_gates, rate, zero, one, zero, channels=C,
+                       blocks=B, taps=taps, decay_scale=8.0, y_off=0, x_off=C)
+        if t % 50 == 49 or t < 3:
+            close(out[0], want[t], 2e-5)
+    assert float(want[399].abs().max()) > 1.0                  # the first input is still there
+
+
+# -- attention over a window and pooled blocks ------------------------------------------------------
+def _attention_case(H, G, D, V, window, pool, rot, base, scale, seed):
+    W = H * D + G * D + G * V
+    eye = torch.eye(W)
+    w = {"m.q": eye[:H * D], "m.k": eye[H * D:(H + G) * D], "m.v": eye[(H + G) * D:],
+         "m.q.norm": rnd(D, seed=seed, std=0.3) + 1.0, "m.k.norm": rnd(D, seed=seed + 1, std=0.3) + 1.0,
+         "m.o": torch.eye(H * V)}
+    m = {"heads": H, "kv_heads": G, "dim": D, "vdim": V, "scale": scale,
+         "mask": {"size": window, "pool": pool}, "rot": {"base": base, "dims": rot}}
+    return W, w, m
+
+
+def _frequencies(base, dims):
+    return torch.tensor([base ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=F64).float()
+
+
+@pytest.mark.parametrize("dtype, tol", [(F32, 1e-5), (BF16, 3e-2)])
+@pytest.mark.parametrize("H, G, D, V, window, pool, rot", [
+    (4, 2, 24, 16, 21, 5, 12), (1, 1, 32, 32, 9, 1, 0), (2, 2, 8, 6, 1, 4, 8),
+    (8, 2, 64, 64, 48, 16, 32), (4, 4, 128, 96, 40, 8, 128), (3, 1, 20, 258, 17, 3, 4)])
+def test_pooled_window_attention(ops, dtype, tol, H, G, D, V, window, pool, rot):
+    """Two requests whose pages are scattered over the pool (the second starts in the middle of
+    the first's run), in portions that end inside pages, windows and blocks; then single tokens.
+    Every position is compared."""
+    W, w, m = _attention_case(H, G, D, V, window, pool, rot, 300.0, 1.3 / math.sqrt(D), 40)
+    w64 = {k: v.double() for k, v in w.items()}
+    eps, page = 1e-5, 16
+    rows = {"a": rnd(150, W, seed=41), "b": rnd(77, W, seed=42)}
+    if dtype == BF16:
+        rows = {r: h.to(BF16).float() for r, h in rows.items()}
+    want = {r: P.pooled_window_attention(h.double(), w64, "m.", m, eps) for r, h in rows.items()}
+    n_pages, max_pages = 24, 10
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(43)).tolist()
+    cperm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(44)).tolist()
+    table = torch.full((2, max_pages), -1, dtype=I32)
+    ctable = torch.full((2, max_pages), -1, dtype=I32)
+    table[0], table[1] = torch.tensor(perm[:10]), torch.tensor(perm[10:20])
+    ctable[0], ctable[1] = torch.tensor(cperm[:10]), torch.tensor(cperm[10:20])
+    table, ctable = dev(table, ctable)
+    fine = torch.full((n_pages, G, page, D + V), float("nan"), dtype=dtype, device=DEV)
+    coarse = torch.full((n_pages, G, page, D + V), float("nan"), dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=I32, device=DEV)
+    fq = dev(_frequencies(300.0, rot)) if rot else None
+    fv = dev(_frequencies(300.0, V))
+    wq, wk = dev(w["m.q.norm"], w["m.k.norm"])
+    plan = [[("a", 37)], [("a", 2), ("b", 30)], [("b", 1), ("a", 58)], [("a", 1), ("b", 1)],
+            [("b", 45), ("a", 1)], [("a", 1)], [("a", 50)]]
+    fed = {"a": 0, "b": 0}
+    idx = {"a": 0, "b": 1}
+    for step in plan:
+        proj = dev(torch.cat([rows[r][fed[r]:fed[r] + k] for r, k in step]))
+        T = proj.shape[0]
+        tok_pos = ints(p for r, k in step for p in range(fed[r], fed[r] + k))
+        tok_req = ints(idx[r] for r, k in step for _ in range(k))
+        q = torch.zeros(T, H * D, device=DEV)
+        sizes = dict(n_heads=H, n_kv_heads=G, head_dim=D, value_dim=V, page_size=page, status=status)
+        ops.pooled_prepare(q, fine, proj, wq, wk, fq, fv, table, tok_pos, tok_req, rot_dims=rot,
+                           eps=eps, writes=True, **sizes)
+        ops.pooled_means(coarse, ctable, fine, table, tok_pos, tok_req, n_kv_heads=G, row=D + V,
+                         block=pool, page_size=page, status=status)
+        out = torch.zeros(T, H * V, dtype=dtype, device=DEV)
+        ops.pooled_attention(out, q, fine, table, coarse, ctable, tok_pos, tok_req, fv,
+                             window=window, block=pool, scale=m["scale"], **sizes)
+        at = 0
+        for r, k in step:
+            close(out[at:at + k], want[r][fed[r]:fed[r] + k], tol)
+            fed[r] += k
+            at += k
+    assert int(status.item()) == 0 and fed == {"a": 150, "b": 77}
+
+
+def test_attention_reports_a_page_that_is_missing(ops):
+    """A table without the page of a position: the status word says so, nothing is written
+    outside the pool and the launch returns."""
+    H = G = 1
+    D = V = 8
+    fine = torch.zeros(2, G, 16, D + V, device=DEV)
+    status = torch.zeros(1, dtype=I32, device=DEV)
+    table = torch.full((1, 2), -1, dtype=I32, device=DEV)
+    proj, q = torch.ones(1, 3 * D, device=DEV), torch.zeros(1, D, device=DEV)
+    ops.pooled_prepare(q, fine, proj, None, None, None, None, table, ints([3]), ints([0]),
+                       n_heads=H, n_kv_heads=G, head_dim=D, value_dim=V, rot_dims=0, eps=1e-5,
+                       writes=True, page_size=16, status=status)
+    assert int(status.item()) != 0 and float(fine.abs().max()) == 0.0
