@@ -283,9 +283,9 @@ PRESETS: dict[str, dict] = {
     ], loop=(1, 3, 2), logit_scale=0.5),
     # layer sizes of a small and a mid-sized production model, few layers: for measurements
     "roritar-1k": _preset(32768, 1024, _layers(
-        6, _attention(16, 4, 64, 64, 1024, 16), {"width": 1024, "blocks": 16, "conv": 4}, 4096)),
+        6, _attention(16, 4, 64, 64, 256, 16), {"width": 1024, "blocks": 16, "conv": 4}, 4096)),
     "roritar-2k": _preset(32768, 2048, _layers(
-        6, _attention(32, 8, 64, 64, 1024, 16), {"width": 2048, "blocks": 16, "conv": 4}, 8192)),
+        6, _attention(32, 8, 64, 64, 256, 16), {"width": 2048, "blocks": 16, "conv": 4}, 8192)),
 }
 
 RORITAR = Architecture(name="Roritar", config_cls=RoritarConfig, build_spec=build_spec,

@@ -153,6 +153,37 @@ def _flops_and_bytes(name, args, kw, batch):
             pairs = idx.shape[0] * idx.shape[1]
             touched = min(E, pairs) * 3 * width * ff * wg.element_size()
             return 2 * pairs * 3 * width * ff, _nbytes(h) + 2 * _nbytes(x) + touched
+        if name == "layernorm_add":
+            x, y = args[:2]
+            return 0, 2 * _nbytes(x) + _nbytes(y, kw.get("out"))
+        if name == "learned_act":
+            return 0, _nbytes(args[0], args[1])
+        if name == "scale_softcap_":
+            return 0, 2 * _nbytes(args[0])
+        if name == "rglru_conv":
+            return 0, 2 * _nbytes(args[0])
+        if name == "rglru_scan":
+            out, _state, u, z = args[:4]
+            return 0, _nbytes(out, u, z) + u.numel() * 4
+        if name == "pooled_prepare":
+            q_out, pool, proj = args[:3]
+            rows = q_out.shape[0] * kw["n_kv_heads"] * (kw["head_dim"] + kw["value_dim"])
+            return 0, _nbytes(q_out) + proj.numel() * 4 + rows * pool.element_size()
+        if name == "pooled_means":
+            pool = args[2]
+            done = sum((start + n) // kw["block"] - start // kw["block"] for start, n in batch)
+            return 0, done * (kw["block"] + 1) * kw["n_kv_heads"] * kw["row"] * pool.element_size()
+        if name == "pooled_attention":
+            out, q, pool = args[:3]
+            H, G, D, V = kw["n_heads"], kw["n_kv_heads"], kw["head_dim"], kw["value_dim"]
+            win, blk = kw["window"], kw["block"]
+            seen = rows = 0
+            for start, n in batch:
+                for i in range(start, start + n):
+                    seen += min(i + 1, win) + max(0, (i - win + 1) // blk)
+                last = start + n - 1
+                rows += last + 1 - max(0, start - win + 1) + max(0, (last - win + 1) // blk)
+            return 2 * H * (D + V) * seen, _nbytes(out, q) + rows * G * (D + V) * pool.element_size()
         if name in ("embed", "scale_", "rotary_pairs", "latent_append", "sample", "argmax",
                     "kv_append"):
             return 0, _nbytes(args[0])
