@@ -15,7 +15,9 @@
 //                     token rows, 32 keys a round (a key per lane for the scores, a column per
 //                     lane for the values), one running softmax over both kinds; the head's
 //                     output is turned back by the query's position and written in the compute
-//                     type
+//                     type.  With a list of tokens (the single-query section of a step's work
+//                     lists) only those are served; the prompt portions then run on the tensor
+//                     cores (attention_pooled_mma.cu)
 //
 // Angles are formed in double and reduced there (rotary.cuh); scores, softmax state and
 // accumulators are float32.  A row's result depends on its own request only: the keys are
@@ -189,6 +191,7 @@ pooled_attention_kernel(TO* __restrict__ out, const float* __restrict__ q,
                         const int* __restrict__ tok_pos, const int* __restrict__ tok_req,
                         const float* __restrict__ freq_v, int n_tokens, int H, int G, int D,
                         int V, int window, int block, float scale, int page_size, int vec,
+                        const int* __restrict__ listed, const int* __restrict__ plan_head,
                         int* __restrict__ status) {
   extern __shared__ float s_q[];                   // [PA_WARPS][max(D, V)]
   pdl_trigger();
@@ -196,8 +199,11 @@ pooled_attention_kernel(TO* __restrict__ out, const float* __restrict__ q,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // consecutive tokens of one head share a block: their windows overlap in the L1
   const long long item = (long long)blockIdx.x * PA_WARPS + warp;
-  if (item >= (long long)n_tokens * H) return;
-  const int h = (int)(item / n_tokens), t = (int)(item - (long long)h * n_tokens);
+  // with a list only the listed tokens are served, as many as the list's head says
+  const int n_here = listed ? min(n_tokens, plan_head[0]) : n_tokens;
+  if (item >= (long long)n_here * H) return;
+  const int h = (int)(item / n_here), entry = (int)(item - (long long)h * n_here);
+  const int t = listed ? listed[3 * entry] : entry;
   const int r = tok_req[t];
   if (r < 0) return;
   const int pos = tok_pos[t];
@@ -351,8 +357,10 @@ HS_EXPORT int hs_pooled_attention(void* out, const float* q, const void* pool, c
                                   const int* tok_pos, const int* tok_req, const float* freq_v,
                                   int n_tokens, int H, int G, int D, int V, int window, int block,
                                   float scale, int page_size, int cache_dtype, int out_dtype,
-                                  int* status, void* stream) {
-  if (!out || !q || !pool || !table || !coarse || !ctable || !tok_pos || !tok_req || !status)
+                                  const int* listed, const int* plan_head, int* status,
+                                  void* stream) {
+  if (!out || !q || !pool || !table || !coarse || !ctable || !tok_pos || !tok_req || !status ||
+      (listed && !plan_head))
     return HS_ERR_ARGUMENT;
   if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0 || V > 1024 || window <= 0 ||
       block <= 0 || page_size <= 0 || (freq_v && V % 2))
@@ -372,7 +380,7 @@ HS_EXPORT int hs_pooled_attention(void* out, const float* q, const void* pool, c
   e = hs_launch(hs::pooled_attention_kernel<TC, TO, C>, grid, blk, smem, st, pdl, (TO*)out, q,   \
                 (const TC*)pool, table, max_pages, num_pages, (const TC*)coarse, ctable,         \
                 cmax_pages, cnum_pages, tok_pos, tok_req, freq_v, n_tokens, H, G, D, V, window,  \
-                block, scale, page_size, vec, status)
+                block, scale, page_size, vec, listed, plan_head, status)
 #define HS_PA_LAUNCH(TC, TO)                                                                     \
   do {                                                                                           \
     if (V <= 64) HS_PA_LAUNCH_C(TC, TO, 2);                                                      \

@@ -222,7 +222,9 @@ def _declare(lib) -> None:
                               I, P, P],
         "hs_pooled_means": [P, P, I, I, P, P, I, I, P, P, I, I, I, I, I, I, P, P],
         "hs_pooled_attention": [P, P, P, P, I, I, P, P, I, I, P, P, P, I, I, I, I, I, I, I, F, I,
-                                I, I, P, P],
+                                I, I, P, P, P, P],
+        "hs_pooled_attention_prefill": [P, P, P, P, I, I, P, P, I, I, P, P, I, P, P, I, I, I, I,
+                                        I, I, F, I, P, P],
         "hs_moe_sorted_scratch": [I, I, I, I, I, I, P, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P, P],
     }
@@ -312,6 +314,7 @@ class CudaOps:
         self._moe_need: dict = {}
         self.latent_mma = True      # prompt portions of latent attention on the tensor cores
         self.biased_mma = True      # prompt portions of the biased chunk attention likewise
+        self.pooled_mma = True      # ... and of the attention over a window and pooled blocks
         self.lightning_bulk_rows = 64   # from this many tokens a step on, lightning attention
         #                                 activates its rows in a pass of their own
         self.latent_splits = None   # blocks a token's keys are split over in latent attention
@@ -1642,10 +1645,13 @@ class CudaOps:
 
     def pooled_attention(self, out, q, pool, table, coarse_pool, coarse_table, tok_pos, tok_req,
                          freq_v, *, n_heads, n_kv_heads, head_dim, value_dim, window, block,
-                         scale, page_size, status):
+                         scale, page_size, status, plan=None):
         """Per token at position i and query head: one softmax over the mean rows of the blocks
         b with b * block + block - 1 <= i - window and the token rows j with 0 <= i - j <
-        window; the output turned back by -i over value_dim (``freq_v`` or None)."""
+        window; the output turned back by -i over value_dim (``freq_v`` or None).  With the
+        step's ``plan`` and a bfloat16 cache the plan's tiles (prompt portions) run on the
+        tensor cores and its single-query tokens on the CUDA cores; without a plan, in float32
+        and for sizes the tile kernel does not take every token runs on the CUDA cores."""
         _want(out, "out", _FLOATS, 2)
         _want(q, "q", torch.float32, 2)
         _want(pool, "pool", _FLOATS)
@@ -1657,13 +1663,32 @@ class CudaOps:
         if out.dtype != pool.dtype:
             raise KernelError("pooled_attention: out has the cache's type")
         per_page = G * page_size * (D + V)
+        listed = head = None
+        if (plan is not None and plan.tile_cap > 0 and out.dtype == torch.bfloat16
+                and self.tensor_cores and self.pooled_mma and plan.n_rows >= T):
+            d = plan.data
+            code = self.lib.hs_pooled_attention_prefill(
+                _ptr(out), _ptr(q), _ptr(pool), _ptr(table), table.shape[1],
+                pool.numel() // per_page, _ptr(coarse_pool), _ptr(coarse_table),
+                coarse_table.shape[1], coarse_pool.numel() // per_page,
+                _ptr(d[4 + plan_decode_ints(plan.n_rows):]), _ptr(d), plan.tile_cap,
+                _ptr(self._scratch_buffer("pooled_counter", 1, torch.int32)), _ptr(freq_v), H, G,
+                D, V, int(window), int(block), float(scale), int(page_size), _ptr(status),
+                self._stream())
+            if code != -1:
+                _check(code, f"pooled_attention_prefill(head_dim={D},value_dim={V})")
+                self.launches += 1
+                if plan.decode_cap == 0:
+                    return
+                listed, head = d[4:], d         # the CUDA-core kernel takes the single tokens
+                T = plan.decode_cap
         self.launches += 1
         _check(self.lib.hs_pooled_attention(
             _ptr(out), _ptr(q), _ptr(pool), _ptr(table), table.shape[1], pool.numel() // per_page,
             _ptr(coarse_pool), _ptr(coarse_table), coarse_table.shape[1],
             coarse_pool.numel() // per_page, _ptr(tok_pos), _ptr(tok_req), _ptr(freq_v), T, H, G,
             D, V, int(window), int(block), float(scale), int(page_size), _DT[pool.dtype],
-            _DT[out.dtype], _ptr(status), self._stream()),
+            _DT[out.dtype], _ptr(listed), _ptr(head), _ptr(status), self._stream()),
             f"pooled_attention(head_dim={D},value_dim={V})")
 
     # -- sampling ---------------------------------------------------------------

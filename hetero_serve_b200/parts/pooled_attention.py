@@ -102,7 +102,8 @@ class PooledWindowAttention(Mixer):
         att = ctx.buffer("pooled_att", (T, self.H * self.V), ctx.dtype)
         ops.pooled_attention(att, q, cache.pool, cache.table, coarse.pool, coarse.table,
                              ctx.tok_pos, ctx.tok_req, self.freq_v, window=self.window,
-                             block=self.pool, scale=self.scale, **sizes)
+                             block=self.pool, scale=self.scale,
+                             plan=getattr(ctx, "plan", None), **sizes)
         ops.linear(x, att, self.w_out, None, residual=None if fresh else x)
 
 

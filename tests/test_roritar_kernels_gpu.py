@@ -191,11 +191,16 @@ def _frequencies(base, dims):
 @pytest.mark.parametrize("dtype, tol", [(F32, 1e-5), (BF16, 3e-2)])
 @pytest.mark.parametrize("H, G, D, V, window, pool, rot", [
     (4, 2, 24, 16, 21, 5, 12), (1, 1, 32, 32, 9, 1, 0), (2, 2, 8, 6, 1, 4, 8),
-    (8, 2, 64, 64, 48, 16, 32), (4, 4, 128, 96, 40, 8, 128), (3, 1, 20, 258, 17, 3, 4)])
-def test_pooled_window_attention(ops, dtype, tol, H, G, D, V, window, pool, rot):
+    (8, 2, 64, 64, 48, 16, 32), (4, 4, 128, 96, 40, 8, 128), (3, 1, 20, 258, 17, 3, 4),
+    (4, 2, 128, 64, 70, 8, 32), (2, 1, 64, 128, 33, 7, 64), (2, 2, 128, 128, 20, 16, 0)])
+@pytest.mark.parametrize("planned", [False, True])
+def test_pooled_window_attention(ops, dtype, tol, H, G, D, V, window, pool, rot, planned):
     """Two requests whose pages are scattered over the pool (the second starts in the middle of
     the first's run), in portions that end inside pages, windows and blocks; then single tokens.
-    Every position is compared."""
+    Every position is compared.  With the step's work lists the portions of a bfloat16 cache run
+    as tiles on the tensor cores where the sizes allow it.  The pages that neither a window nor
+    an unfinished block of the step reaches are taken out of the table: nothing may look them
+    up."""
     W, w, m = _attention_case(H, G, D, V, window, pool, rot, 300.0, 1.3 / math.sqrt(D), 40)
     w64 = {k: v.double() for k, v in w.items()}
     eps, page = 1e-5, 16
@@ -225,16 +230,27 @@ def test_pooled_window_attention(ops, dtype, tol, H, G, D, V, window, pool, rot)
         proj = dev(torch.cat([rows[r][fed[r]:fed[r] + k] for r, k in step]))
         T = proj.shape[0]
         tok_pos = ints(p for r, k in step for p in range(fed[r], fed[r] + k))
-        tok_req = ints(idx[r] for r, k in step for _ in range(k))
+        tok_req = ints(row for row, (r, k) in enumerate(step) for _ in range(k))
+        order = [idx[r] for r, k in step]           # the tables' rows follow the batch
+        tab, ctab = table[order].contiguous(), ctable[order].contiguous()
         q = torch.zeros(T, H * D, device=DEV)
         sizes = dict(n_heads=H, n_kv_heads=G, head_dim=D, value_dim=V, page_size=page, status=status)
-        ops.pooled_prepare(q, fine, proj, wq, wk, fq, fv, table, tok_pos, tok_req, rot_dims=rot,
+        ops.pooled_prepare(q, fine, proj, wq, wk, fq, fv, tab, tok_pos, tok_req, rot_dims=rot,
                            eps=eps, writes=True, **sizes)
-        ops.pooled_means(coarse, ctable, fine, table, tok_pos, tok_req, n_kv_heads=G, row=D + V,
+        for row, (r, k) in enumerate(step):
+            lo = max(0, min(fed[r] - window + 1, fed[r] // pool * pool))
+            tab[row, :lo // page] = -1
+        ops.pooled_means(coarse, ctab, fine, tab, tok_pos, tok_req, n_kv_heads=G, row=D + V,
                          block=pool, page_size=page, status=status)
-        out = torch.zeros(T, H * V, dtype=dtype, device=DEV)
-        ops.pooled_attention(out, q, fine, table, coarse, ctable, tok_pos, tok_req, fv,
-                             window=window, block=pool, scale=m["scale"], **sizes)
+        out = torch.full((T, H * V), float("nan"), dtype=dtype, device=DEV)
+        work = ops.make_plan([(row, row, fed[r], k) for row, (r, k) in enumerate(step)], T, page) \
+            if planned else None
+        before = ops.launches
+        ops.pooled_attention(out, q, fine, tab, coarse, ctab, tok_pos, tok_req, fv,
+                             window=window, block=pool, scale=m["scale"], plan=work, **sizes)
+        if planned and work.tile_cap and work.decode_cap:      # tiles and single tokens apart?
+            tiled = dtype == BF16 and D in (64, 128) and V in (64, 128)
+            assert ops.launches - before == (2 if tiled else 1)
         at = 0
         for r, k in step:
             close(out[at:at + k], want[r][fed[r]:fed[r] + k], tol)
