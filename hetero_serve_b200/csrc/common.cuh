@@ -33,7 +33,9 @@
 #define HS_ACT_GELU_ERF 2
 #define HS_ACT_RELU2 3      // max(u, 0)^2
 #define HS_ACT_SILU 4       // u * sigmoid(u)
-#define HS_ACT_LAST HS_ACT_SILU
+#define HS_ACT_XIELU 5      // u > 0: a u^2 + u/2;  u <= 0: b (e^u - 1 - u) + u/2, with two numbers
+//                             (a, b) that travel with the code
+#define HS_ACT_LAST HS_ACT_XIELU
 
 #define HS_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -93,6 +95,13 @@ __device__ __forceinline__ float apply_act(float u, int act) {
   if (act == HS_ACT_RELU2) { const float r = fmaxf(u, 0.f); return r * r; }
   if (act == HS_ACT_SILU) return u / (1.0f + expf(-u));
   return u;
+}
+__device__ __forceinline__ float xielu(float u, float2 ab) {
+  return u > 0.f ? fmaf(ab.x * u, u, 0.5f * u) : fmaf(ab.y, expm1f(u) - u, 0.5f * u);
+}
+// with the numbers of an activation that has some
+__device__ __forceinline__ float apply_act(float u, int act, float2 ab) {
+  return act == HS_ACT_XIELU ? xielu(u, ab) : apply_act(u, act);
 }
 
 // Phase timing for tuning builds only: compiled in with -DHS_PHASE_MARKS (the build script adds

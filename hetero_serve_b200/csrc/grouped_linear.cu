@@ -65,12 +65,17 @@ grouped_linear_kernel(TO* __restrict__ out, const float* __restrict__ a,
 // one group a block, mma.sync m16n8k16.  The weights come n-major here ([groups, n, k], the
 // summed index fastest); the float32 input slice is rounded to bfloat16 on its way into shared
 // memory (fetched into registers a step ahead), the weights are copied asynchronously.
-template <typename TO>
+// SPLIT == 3: each input number is written as the sum of three bfloat16 terms (its rounding, the
+// rounding of what is left, and again: 24 bits in all, a float32's whole mantissa) and the three
+// products are summed in the same float32 accumulators.  A product of two bfloat16 numbers is
+// exact in float32, so with weights that ARE bfloat16 numbers the result is the float32 product
+// up to the order of its additions.
+template <typename TO, int SPLIT>
 __global__ void __launch_bounds__(128)
 grouped_linear_mma_kernel(TO* __restrict__ out, const float* __restrict__ a,
                           const __nv_bfloat16* __restrict__ w, int n_tokens, int a_stride,
                           int a_off, int a_gstride, int groups, int N, int K, int vec) {
-  __shared__ __align__(16) __nv_bfloat16 s_a[2][TM * TS];
+  __shared__ __align__(16) __nv_bfloat16 s_a[2][SPLIT][TM * TS];
   __shared__ __align__(16) __nv_bfloat16 s_b[2][TN * TS];
   const int t0 = blockIdx.x * TM, n0 = blockIdx.y * TN, g = blockIdx.z;
   const int rows = min(TM, n_tokens - t0), ncols = min(TN, N - n0);
@@ -104,10 +109,19 @@ grouped_linear_mma_kernel(TO* __restrict__ out, const float* __restrict__ a,
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int c = threadIdx.x + 128 * j;
-      __nv_bfloat162 p[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(ra[j][2 * i], ra[j][2 * i + 1]);
-      *(uint4*)(s_a[buf] + (c >> 2) * TS + (c & 3) * 8) = *(const uint4*)p;
+      for (int term = 0; term < SPLIT; ++term) {
+        __nv_bfloat162 p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          p[i] = __floats2bfloat162_rn(ra[j][2 * i], ra[j][2 * i + 1]);
+          if (term + 1 < SPLIT) {              // what this term leaves for the next (exact)
+            ra[j][2 * i] -= __bfloat162float(p[i].x);
+            ra[j][2 * i + 1] -= __bfloat162float(p[i].y);
+          }
+        }
+        *(uint4*)(s_a[buf][term] + (c >> 2) * TS + (c & 3) * 8) = *(const uint4*)p;
+      }
     }
   };
   float acc[2][4][4];
@@ -137,19 +151,23 @@ grouped_linear_mma_kernel(TO* __restrict__ out, const float* __restrict__ a,
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < TK; kk += 16) {
-      uint32_t fa[2][4];
+      uint32_t fb[2][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
-        ldmatrix_x4(fa[i], s_a[buf] + (wm + 16 * i + a_r) * TS + kk + a_c);
+      for (int j = 0; j < 2; ++j)
+        ldmatrix_x4(fb[j], s_b[buf] + (wn + 16 * j + b_r) * TS + kk + b_c);
 #pragma unroll
-      for (int j = 0; j < 4; j += 2) {
-        uint32_t fb[4];
-        ldmatrix_x4(fb, s_b[buf] + (wn + 8 * j + b_r) * TS + kk + b_c);
+      for (int term = SPLIT - 1; term >= 0; --term) {      // the small terms first
+        uint32_t fa[2][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          mma_bf16(acc[i][j], fa[i], fb);
-          mma_bf16(acc[i][j + 1], fa[i], fb + 2);
-        }
+        for (int i = 0; i < 2; ++i)
+          ldmatrix_x4(fa[i], s_a[buf][term] + (wm + 16 * i + a_r) * TS + kk + a_c);
+#pragma unroll
+        for (int j = 0; j < 4; j += 2)
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            mma_bf16(acc[i][j], fa[i], fb[j >> 1]);
+            mma_bf16(acc[i][j + 1], fa[i], fb[j >> 1] + 2);
+          }
       }
     }
     if (more) store_a(buf ^ 1);      // that stage was last read a turn ago, behind a barrier
@@ -206,19 +224,26 @@ HS_EXPORT int hs_grouped_linear(void* out, const float* a, const void* w, int n_
 // HS_ERR_UNSUPPORTED for what it does not take (the caller then uses the kernel above).
 HS_EXPORT int hs_grouped_linear_mma(void* out, const float* a, const void* w_nk, int n_tokens,
                                     int a_stride, int a_off, int a_gstride, int groups, int n,
-                                    int k, int out_dtype, void* stream) {
+                                    int k, int out_dtype, int split, void* stream) {
   if (!out || !a || !w_nk) return HS_ERR_ARGUMENT;
-  if (groups <= 0 || n <= 0 || k <= 0 || k % hs::TK) return HS_ERR_UNSUPPORTED;
+  if (groups <= 0 || n <= 0 || k <= 0 || k % hs::TK || (split != 1 && split != 3))
+    return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
   const int vec = a_stride % 4 == 0 && a_off % 4 == 0 && a_gstride % 4 == 0 && !((uintptr_t)a & 15);
   dim3 grid((n_tokens + hs::TM - 1) / hs::TM, (n + hs::TN - 1) / hs::TN, groups);
   cudaStream_t st = (cudaStream_t)stream;
-  if (out_dtype == HS_DT_F32)
-    hs::grouped_linear_mma_kernel<float><<<grid, 128, 0, st>>>(
+  if (out_dtype == HS_DT_F32 && split == 3)
+    hs::grouped_linear_mma_kernel<float, 3><<<grid, 128, 0, st>>>(
+        (float*)out, a, (const __nv_bfloat16*)w_nk, n_tokens, a_stride, a_off, a_gstride, groups,
+        n, k, vec);
+  else if (split == 3)
+    return HS_ERR_UNSUPPORTED;
+  else if (out_dtype == HS_DT_F32)
+    hs::grouped_linear_mma_kernel<float, 1><<<grid, 128, 0, st>>>(
         (float*)out, a, (const __nv_bfloat16*)w_nk, n_tokens, a_stride, a_off, a_gstride, groups,
         n, k, vec);
   else if (out_dtype == HS_DT_BF16)
-    hs::grouped_linear_mma_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
+    hs::grouped_linear_mma_kernel<__nv_bfloat16, 1><<<grid, 128, 0, st>>>(
         (__nv_bfloat16*)out, a, (const __nv_bfloat16*)w_nk, n_tokens, a_stride, a_off, a_gstride,
         groups, n, k, vec);
   else

@@ -35,7 +35,7 @@ template <typename TI, typename TO, bool VEC>
 __global__ void __launch_bounds__(LS_THREADS)
 linear_simt_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
                    const float* __restrict__ bias, const float* residual, int M, int N, int K,
-                   int act) {
+                   int act, float2 ab) {
   __shared__ float As[LS_BK][LS_BM + 4];
   __shared__ float Ws[LS_BK][LS_BN + 4];
   const int tid = threadIdx.x;
@@ -96,7 +96,7 @@ linear_simt_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
       if (gn >= N) continue;
       float v = acc[i][j];
       if (bias) v += bias[gn];
-      v = apply_act(v, act);
+      v = apply_act(v, act, ab);
       if (residual) v += residual[(size_t)gm * N + gn];
       out[(size_t)gm * N + gn] = from_f<TO>(v);
     }
@@ -116,7 +116,7 @@ template <typename TI, typename TO, bool VEC>
 __global__ void __launch_bounds__(LB_THREADS)
 linear_simt_big_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
                        const float* __restrict__ bias, const float* residual, int M, int N, int K,
-                       int act) {
+                       int act, float2 ab) {
   __shared__ __align__(16) float As[2][LB_BK][LB_BM];
   __shared__ __align__(16) float Ws[2][LB_BK][LB_BN];
   const int tid = threadIdx.x;
@@ -192,7 +192,7 @@ linear_simt_big_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__
       if (gn >= N) continue;
       float v = acc[i][j];
       if (bias) v += bias[gn];
-      v = apply_act(v, act);
+      v = apply_act(v, act, ab);
       if (residual) v += residual[(size_t)gm * N + gn];
       out[(size_t)gm * N + gn] = from_f<TO>(v);
     }
@@ -238,7 +238,7 @@ template <typename TI, typename TO, int RPT>
 __global__ void __launch_bounds__(LF_THREADS)
 linear_simt_few_rows_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
                             const float* __restrict__ bias, const float* residual, int M, int N,
-                            int K, int act) {
+                            int K, int act, float2 ab) {
   using S = LfShape<TI, RPT>;
   extern __shared__ __align__(16) uint8_t lf_smem[];
   TI* ring = (TI*)lf_smem;
@@ -301,7 +301,7 @@ linear_simt_few_rows_kernel(TO* out, const TI* __restrict__ a, const TI* __restr
     if (gm >= M) continue;
     float v = acc[r];
     if (bias) v += bias[gn];
-    v = apply_act(v, act);
+    v = apply_act(v, act, ab);
     if (residual) v += residual[(size_t)gm * N + gn];
     out[(size_t)gm * N + gn] = from_f<TO>(v);
   }
@@ -309,7 +309,7 @@ linear_simt_few_rows_kernel(TO* out, const TI* __restrict__ a, const TI* __restr
 
 template <typename TI, typename TO, int RPT>
 static int launch_few_rows_as(void* out, const void* a, const void* w, const float* bias,
-                              const float* residual, int M, int N, int K, int act,
+                              const float* residual, int M, int N, int K, int act, float2 ab,
                               cudaStream_t st) {
   auto* k = linear_simt_few_rows_kernel<TI, TO, RPT>;
   static cudaError_t state = cudaErrorUnknown;
@@ -318,22 +318,23 @@ static int launch_few_rows_as(void* out, const void* a, const void* w, const flo
                                  (int)LfShape<TI, RPT>::SMEM);
   if (state != cudaSuccess) return (int)state;
   k<<<(N + LF_BN - 1) / LF_BN, LF_THREADS, LfShape<TI, RPT>::SMEM, st>>>(
-      (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);
+      (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act, ab);
   return HS_OK;
 }
 
 template <typename TI, typename TO>
 static int launch_few_rows(void* out, const void* a, const void* w, const float* bias,
-                           const float* residual, int M, int N, int K, int act, cudaStream_t st) {
-  if (M <= 16) return launch_few_rows_as<TI, TO, 2>(out, a, w, bias, residual, M, N, K, act, st);
-  return launch_few_rows_as<TI, TO, 8>(out, a, w, bias, residual, M, N, K, act, st);
+                           const float* residual, int M, int N, int K, int act, float2 ab, cudaStream_t st) {
+  if (M <= 16) return launch_few_rows_as<TI, TO, 2>(out, a, w, bias, residual, M, N, K, act, ab, st);
+  return launch_few_rows_as<TI, TO, 8>(out, a, w, bias, residual, M, N, K, act, ab, st);
 }
 
 }  // namespace hs
 
 HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const float* bias,
-                             const float* residual, int M, int N, int K, int act, int in_dtype,
-                             int out_dtype, void* stream) {
+                             const float* residual, int M, int N, int K, int act, float act_a,
+                             float act_b, int in_dtype, int out_dtype, void* stream) {
+  const float2 ab = make_float2(act_a, act_b);
   if (!out || !a || !w) return HS_ERR_ARGUMENT;
   if (M <= 0 || N <= 0) return HS_OK;
   if (K <= 0) return HS_ERR_ARGUMENT;
@@ -350,11 +351,11 @@ HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const floa
   if (few && K % vec == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15)) {
     int rc = HS_ERR_UNSUPPORTED;
     if (in_dtype == HS_DT_F32 && out_dtype == HS_DT_F32)
-      rc = hs::launch_few_rows<float, float>(out, a, w, bias, residual, M, N, K, act, st);
+      rc = hs::launch_few_rows<float, float>(out, a, w, bias, residual, M, N, K, act, ab, st);
     else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_BF16)
-      rc = hs::launch_few_rows<bf16, bf16>(out, a, w, bias, residual, M, N, K, act, st);
+      rc = hs::launch_few_rows<bf16, bf16>(out, a, w, bias, residual, M, N, K, act, ab, st);
     else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_F32)
-      rc = hs::launch_few_rows<bf16, float>(out, a, w, bias, residual, M, N, K, act, st);
+      rc = hs::launch_few_rows<bf16, float>(out, a, w, bias, residual, M, N, K, act, ab, st);
     if (rc != HS_OK) return rc;
     HS_LAUNCH_CHECK();
     return HS_OK;
@@ -367,10 +368,10 @@ HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const floa
   do {                                                                                         \
     if (vec4)                                                                                  \
       hs::linear_simt_big_kernel<TI, TO, true><<<big, hs::LB_THREADS, 0, st>>>(                \
-          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);                 \
+          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act, ab);                 \
     else                                                                                       \
       hs::linear_simt_big_kernel<TI, TO, false><<<big, hs::LB_THREADS, 0, st>>>(               \
-          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);                 \
+          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act, ab);                 \
   } while (0)
     if (in_dtype == HS_DT_F32 && out_dtype == HS_DT_F32) HS_LB_LAUNCH(float, float);
     else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_BF16) HS_LB_LAUNCH(bf16, bf16);
@@ -385,10 +386,10 @@ HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const floa
   do {                                                                                        \
     if (ls_vec)                                                                               \
       hs::linear_simt_kernel<TI, TO, true><<<grid, hs::LS_THREADS, 0, st>>>(                  \
-          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);                \
+          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act, ab);                \
     else                                                                                      \
       hs::linear_simt_kernel<TI, TO, false><<<grid, hs::LS_THREADS, 0, st>>>(                 \
-          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);                \
+          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act, ab);                \
   } while (0)
   if (in_dtype == HS_DT_F32 && out_dtype == HS_DT_F32) HS_LS_LAUNCH(float, float);
   else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_BF16) HS_LS_LAUNCH(bf16, bf16);

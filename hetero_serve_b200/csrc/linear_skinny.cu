@@ -55,6 +55,7 @@ struct SkinnyParams {
   float* partial;              // [ksplit][MP][N] float32 scratch (ksplit > 1)
   int* counters;               // one per feature block, zero between launches (ksplit > 1)
   int M, N, K, act, out_f32;
+  float2 act_ab;           // the numbers of an activation that has some
   int kper, stride;            // k per CTA (multiple of 32); smem row stride in elements
   int red_offset;              // bytes from the start of shared memory to the reduction tiles
   int ng;                      // feature groups (of 16) per feature block: 1, 2, 4 or 8
@@ -422,7 +423,7 @@ linear_skinny_kernel(const typename SkinnyParamsOf<ARGMAX>::type p) {
     }
     const bool first = first_fb && i == my_e;            // bias (and residual) already in registers
     if (p.bias) v += first ? my_bias : p.bias[n];
-    v = apply_act(v, p.act);
+    v = apply_act(v, p.act, p.act_ab);
     if (p.residual) v += (first && ksplit == 1) ? my_res : p.residual[(size_t)m * p.N + n];
     if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n] = v;
     else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
@@ -667,7 +668,8 @@ HS_EXPORT int hs_linear_skinny_scratch(int M, int N, int K, int with_norm, long 
 // caller then uses another kernel.
 HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const float* gamma,
                                const float* beta, float eps, const void* w, const float* bias,
-                               const float* residual, int M, int N, int K, int act, int out_dtype,
+                               const float* residual, int M, int N, int K, int act, float act_a,
+                               float act_b, int out_dtype,
                                float* scratch, int* counters, int pdl, void* stream) {
   using namespace hs;
   if (!out || !w || (!a && !x)) return HS_ERR_ARGUMENT;
@@ -686,6 +688,7 @@ HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const f
   p.w = (const __nv_bfloat16*)w; p.bias = bias; p.residual = residual; p.out = out;
   p.partial = scratch; p.counters = counters;
   p.M = M; p.N = N; p.K = K; p.act = act; p.out_f32 = out_dtype == HS_DT_F32;
+  p.act_ab = make_float2(act_a, act_b);
   p.kper = pl.kper; p.stride = pl.stride; p.ng = pl.ng; p.eps = eps;
   p.red_offset = pl.red_offset;
   p.timing = hs_timing_buffer();
@@ -735,6 +738,7 @@ HS_EXPORT int hs_linear_skinny_argmax(float* out, const void* a, const void* w, 
   p.w = (const __nv_bfloat16*)w; p.bias = nullptr; p.residual = nullptr; p.out = out;
   p.partial = nullptr; p.counters = nullptr;
   p.M = M; p.N = N; p.K = K; p.act = HS_ACT_NONE; p.out_f32 = 1;
+  p.act_ab = make_float2(0.f, 0.f);
   p.kper = pl.kper; p.stride = pl.stride; p.ng = pl.ng; p.eps = 0.f;
   p.red_offset = pl.red_offset;
   p.tokens = tokens; p.feedback = feedback; p.feedback_slot = feedback_slot;

@@ -61,6 +61,7 @@ struct TcParams {
   int* counters;         // one per output tile, zero between launches (splits > 1)
   int* status;
   int M, N, K, act;
+  float2 act_ab;           // the numbers of an activation that has some
   int tiles_m, tiles_n;
   int splits, kb_per_split;   // k blocks (of 64) per split
 };
@@ -150,6 +151,9 @@ __device__ __forceinline__ void finish_row32(const TcParams& p, const uint32_t (
   } else if (p.act == HS_ACT_SILU) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_SILU);
+  } else if (p.act == HS_ACT_XIELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = xielu(f[j], p.act_ab);
   }
   const size_t off = (size_t)row * p.N + nbase;
   if (p.residual) {
@@ -201,6 +205,9 @@ __device__ __forceinline__ void bias_act32(const TcParams& p, const uint32_t (&v
   } else if (p.act == HS_ACT_SILU) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_SILU);
+  } else if (p.act == HS_ACT_XIELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = xielu(f[j], p.act_ab);
   }
 }
 
@@ -556,6 +563,9 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
               } else if (p.act == HS_ACT_SILU) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_SILU);
+              } else if (p.act == HS_ACT_XIELU) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] = xielu(x[j], p.act_ab);
               }
               if (p.residual) {
                 x[0] += r4.x; x[1] += r4.y; x[2] += r4.z; x[3] += r4.w;
@@ -599,7 +609,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             for (int j = 0; j < 4; ++j) {
               if (n + j < p.N) {
                 float x = vals[j] + (p.bias ? p.bias[n + j] : 0.f);
-                x = act_tc(x, p.act);
+                x = p.act == HS_ACT_XIELU ? xielu(x, p.act_ab) : act_tc(x, p.act);
                 if (p.residual) x += p.residual[off + j];
                 out[off + j] = from_f<TO>(x);
               }
@@ -1008,6 +1018,9 @@ linear_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_a,
       } else if (p.act == HS_ACT_SILU) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_SILU);
+      } else if (p.act == HS_ACT_XIELU) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = xielu(x[j], p.act_ab);
       }
       x[0] += r4.x; x[1] += r4.y; x[2] += r4.z; x[3] += r4.w;
       if (vec4) {
@@ -1302,7 +1315,7 @@ HS_EXPORT void hs_set_split_clusters(int on) { hs::g_split_clusters = on != 0; }
 // back to the CUDA-core kernel.
 HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const float* bias,
                                 const float* residual, int M, int N, int K, int act,
-                                int out_dtype, int tile_n, int pair, float* scratch,
+                                float act_a, float act_b, int out_dtype, int tile_n, int pair, float* scratch,
                                 int* counters, int* status, void* stream) {
   using namespace hs;
   if (!out || !a || !w || !status) return HS_ERR_ARGUMENT;
@@ -1323,6 +1336,7 @@ HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const f
   TcParams p;
   p.out = out; p.bias = bias; p.residual = residual; p.partial = scratch; p.counters = counters;
   p.status = status; p.M = M; p.N = N; p.K = K; p.act = act;
+  p.act_ab = make_float2(act_a, act_b);
   p.tiles_m = pl.tiles_m; p.tiles_n = pl.tiles_n; p.splits = pl.splits;
   p.kb_per_split = pl.kb_per_split;
   cudaStream_t st = (cudaStream_t)stream;

@@ -127,6 +127,74 @@ rglru_scan_kernel(TO* __restrict__ out, float* __restrict__ state, int state_str
   }
 }
 
+// One token of every request: convolution, gates, decay, the state's step and the history in
+// ONE launch.  A block takes one (token, part of the channels): the part's n convolved inputs go
+// to shared memory, the 2n gate sums are formed from them as the block-diagonal kernel forms
+// them (four warps each sum a quarter of the inputs for 32 columns at a time, the quarters are
+// added in the same order), then a thread per channel steps the state.  Every sum has the order
+// it has on the path of three launches, so a token's result is the same bits on both.
+constexpr int RS_THREADS = 128;
+
+template <typename TO>
+__global__ void __launch_bounds__(RS_THREADS)
+rglru_step_kernel(TO* __restrict__ out, float* __restrict__ state, int state_stride,
+                  const float* __restrict__ proj, int proj_stride, int y_off, int x_off,
+                  const float* __restrict__ cw, const float* __restrict__ cb,
+                  const float* __restrict__ w_gates, const float* __restrict__ b_gates,
+                  const float* __restrict__ rate, const int* __restrict__ tok_req,
+                  const int* __restrict__ req_slot, int C, int n_per, int taps, float scale) {
+  extern __shared__ float s_rs[];                  // u [n_per] | partial sums [4][2 n_per]
+  float* s_u = s_rs;
+  float* s_z = s_rs + n_per;
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.y, blk = blockIdx.x;
+  const int r = tok_req[t];
+  if (r < 0) return;
+  float* st = state + (size_t)req_slot[r] * state_stride;
+  float* hist = st + C;                            // [taps-1][C], oldest first
+  const float* row = proj + (size_t)t * proj_stride;
+  const int c0 = blk * n_per;
+  for (int i = threadIdx.x; i < n_per; i += RS_THREADS) {
+    const int c = c0 + i;
+    float acc = cb[c];
+    for (int j = 0; j < taps; ++j) {
+      const float v = j == 0 ? row[x_off + c] : hist[(size_t)(taps - 1 - j) * C + c];
+      acc = fmaf(cw[(size_t)c * taps + (taps - 1 - j)], v, acc);
+    }
+    s_u[i] = acc;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_out = 2 * n_per;
+  const int per = (n_per + 3) / 4;
+  const int k_lo = warp * per, k_hi = min(n_per, k_lo + per);
+  const float* wg = w_gates + (size_t)blk * n_per * n_out;
+  for (int j0 = 0; j0 < n_out; j0 += 32) {
+    const int j = j0 + lane;
+    float acc = 0.f;
+    if (j < n_out) {
+#pragma unroll 8
+      for (int kk = k_lo; kk < k_hi; ++kk) acc = fmaf(s_u[kk], wg[(size_t)kk * n_out + j], acc);
+      s_z[warp * n_out + j] = acc;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_per; i += RS_THREADS) {
+    const int c = c0 + i;
+    const float zr = ((s_z[i] + s_z[n_out + i]) + s_z[2 * n_out + i]) + s_z[3 * n_out + i];
+    const float zi = ((s_z[n_per + i] + s_z[n_out + n_per + i]) + s_z[2 * n_out + n_per + i]) +
+                     s_z[3 * n_out + n_per + i];
+    const int zc = blk * n_out + i;
+    const RgStep s = rg_step(zr + b_gates[zc], zi + b_gates[zc + n_per], s_u[i], rate[c], scale);
+    const float S = fmaf(s.a, st[c], s.d);
+    out[(size_t)t * C + c] = from_f<TO>(S * gelu_tanh(row[y_off + c]));
+    st[c] = S;
+    for (int k = 0; k + 1 < taps - 1; ++k) hist[(size_t)k * C + c] = hist[(size_t)(k + 1) * C + c];
+    if (taps > 1) hist[(size_t)(taps - 2) * C + c] = row[x_off + c];
+  }
+}
+
 }  // namespace hs
 
 HS_EXPORT int hs_rglru_conv(float* u, const float* proj, int proj_stride, int x_off,
@@ -168,6 +236,40 @@ HS_EXPORT int hs_rglru_scan(void* out, float* state, int state_stride, const flo
     e = hs_launch(hs::rglru_scan_kernel<float>, grid, block, 0, st, hs_pdl_enabled(),
                   (float*)out, state, state_stride, u, z, proj, proj_stride, y_off, x_off,
                   b_gates, rate, req_start, req_len, req_slot, C, C / blocks, taps, scale);
+  else
+    return HS_ERR_UNSUPPORTED;
+  return e == cudaSuccess ? HS_OK : (int)e;
+}
+
+// One token a request (tokens whose request row is negative are skipped).  The gate matrices
+// are float32 [blocks, n (summed), 2n (r | i)].  Refuses parts too large for shared memory.
+HS_EXPORT int hs_rglru_step(void* out, float* state, int state_stride, const float* proj,
+                            int proj_stride, int y_off, int x_off, const float* cw,
+                            const float* cb, const float* w_gates, const float* b_gates,
+                            const float* rate, const int* tok_req, const int* req_slot,
+                            int n_tokens, int C, int blocks, int taps, float scale, int out_dtype,
+                            void* stream) {
+  if (!out || !state || !proj || !cw || !cb || !w_gates || !b_gates || !rate || !tok_req ||
+      !req_slot)
+    return HS_ERR_ARGUMENT;
+  if (C <= 0 || blocks <= 0 || C % blocks || taps < 1 || state_stride < C * taps)
+    return HS_ERR_UNSUPPORTED;
+  const int n_per = C / blocks;
+  const size_t smem = (size_t)9 * n_per * sizeof(float);
+  if (smem > 40 * 1024) return HS_ERR_UNSUPPORTED;
+  if (n_tokens <= 0) return HS_OK;
+  if (n_tokens > 65535) return HS_ERR_TOO_LARGE;
+  const dim3 grid(blocks, n_tokens), block(hs::RS_THREADS);
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+  if (out_dtype == HS_DT_BF16)
+    e = hs_launch(hs::rglru_step_kernel<__nv_bfloat16>, grid, block, smem, st, hs_pdl_enabled(),
+                  (__nv_bfloat16*)out, state, state_stride, proj, proj_stride, y_off, x_off, cw,
+                  cb, w_gates, b_gates, rate, tok_req, req_slot, C, n_per, taps, scale);
+  else if (out_dtype == HS_DT_F32)
+    e = hs_launch(hs::rglru_step_kernel<float>, grid, block, smem, st, hs_pdl_enabled(),
+                  (float*)out, state, state_stride, proj, proj_stride, y_off, x_off, cw, cb,
+                  w_gates, b_gates, rate, tok_req, req_slot, C, n_per, taps, scale);
   else
     return HS_ERR_UNSUPPORTED;
   return e == cudaSuccess ? HS_OK : (int)e;

@@ -24,6 +24,16 @@ from . import build as _build
 ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2, "relu2": 3, "silu": 4}
 # activations with learned numbers (how many): applied by ``learned_act`` between two linears
 LEARNED_ACTIVATIONS = {"xielu": 2}
+_LEARNED_CODES = {"xielu": 5}
+
+
+def learned_constants(act: str, values) -> tuple[float, float]:
+    """The two numbers a kernel takes for an activation with learned numbers.  xielu, values
+    (p, q): softplus(p) and 1/2 + softplus(q), formed in double."""
+    if act != "xielu" or len(values) != LEARNED_ACTIVATIONS["xielu"]:
+        raise KernelError(f"activation {act!r} with {len(values)} numbers not taken")
+    sp = lambda v: math.log1p(math.exp(-abs(v))) + max(v, 0.0)      # softplus
+    return sp(values[0]), 0.5 + sp(values[1])
 EXPERT_ACTIVATIONS = {"clamped": 0, "silu": 1}
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -169,10 +179,10 @@ def _declare(lib) -> None:
     sig = {
         "hs_embed": [P, P, P, P, P, P, I, I, I, I, I, P, I, F, P, P],
         "hs_layernorm": [P, P, P, P, P, I, I, F, I, P],
-        "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
-        "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, I, P, P, P, P],
+        "hs_linear_simt": [P, P, P, P, P, I, I, I, I, F, F, I, I, P],
+        "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, F, F, I, I, I, P, P, P, P],
         "hs_linear_tcgen05_scratch": [I, I, I, I, I, P, P],
-        "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, I, P, P, I, P],
+        "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, F, F, I, P, P, I, P],
         "hs_linear_skinny_scratch": [I, I, I, I, P, P],
         "hs_linear_skinny_argmax": [P, P, P, I, I, I, P, P, P, P, P, P, P, I, P],
         "hs_linear_skinny_argmax_scratch": [I, I, I, P],
@@ -191,7 +201,7 @@ def _declare(lib) -> None:
         "hs_scale": [P, ctypes.c_longlong, F, P],
         "hs_rotary_pairs": [P, P, P, P, I, I, I, I, I, I, P],
         "hs_grouped_linear": [P, P, P, I, I, I, I, I, I, I, I, I, P],
-        "hs_grouped_linear_mma": [P, P, P, I, I, I, I, I, I, I, I, P],
+        "hs_grouped_linear_mma": [P, P, P, I, I, I, I, I, I, I, I, I, P],
         "hs_latent_append": [P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, P, P, I, P],
         "hs_latent_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I,
                                 P, P, I, P, P],
@@ -218,6 +228,7 @@ def _declare(lib) -> None:
         "hs_scale_softcap": [P, ctypes.c_longlong, F, F, P],
         "hs_rglru_conv": [P, P, I, I, P, P, P, I, P, P, P, I, I, I, P],
         "hs_rglru_scan": [P, P, I, P, P, P, I, I, I, P, P, P, P, P, I, I, I, I, F, I, P],
+        "hs_rglru_step": [P, P, I, P, I, I, I, P, P, P, P, P, P, P, I, I, I, I, F, I, P],
         "hs_pooled_prepare": [P, P, P, I, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, I,
                               I, P, P],
         "hs_pooled_means": [P, P, I, I, P, P, I, I, P, P, I, I, I, I, I, I, P, P],
@@ -441,8 +452,10 @@ class CudaOps:
                f"layernorm(width={width})")
 
     # -- linear ---------------------------------------------------------------
-    def linear(self, out, a, w, bias=None, act="none", residual=None):
-        """out = act(a @ w.T + bias) (+ residual).  a [M,K], w [N,K], out [M,N].
+    def linear(self, out, a, w, bias=None, act="none", residual=None, act_values=()):
+        """out = act(a @ w.T + bias) (+ residual).  a [M,K], w [N,K], out [M,N].  ``act`` is one
+        of ACTIVATIONS, or of LEARNED_ACTIVATIONS with its learned numbers in ``act_values``
+        (applied to the float32 sum, as ``learned_act`` does).
 
         ``residual`` is float32 [M,N] and may be ``out`` itself (accumulate in place)."""
         _want(a, "a", _FLOATS, 2)
@@ -463,16 +476,25 @@ class CudaOps:
             _want(residual, "residual", torch.float32, 2)
             if tuple(residual.shape) != (M, N):
                 raise KernelError("linear: residual shape != out shape")
-        if act not in ACTIVATIONS:
+        if act in LEARNED_ACTIVATIONS:
+            if len(act_values) != LEARNED_ACTIVATIONS[act]:
+                raise KernelError(f"linear: activation {act!r} takes "
+                                  f"{LEARNED_ACTIVATIONS[act]} numbers")
+            code = (_LEARNED_CODES[act], *learned_constants(act, act_values))
+        elif act in ACTIVATIONS:
+            code = (ACTIVATIONS[act], 0.0, 0.0)
+        else:
             raise KernelError(f"linear: unknown activation {act!r}")
-        self._linear(out, a, w, bias, ACTIVATIONS[act], residual, M, N, K)
+        self._linear(out, a, w, bias, code, residual, M, N, K)
 
     def _linear(self, out, a, w, bias, act, residual, M, N, K):
-        """bfloat16 goes to the tcgen05 kernel when TMA can address the operands (K a multiple
+        """``act`` is a code of ACTIVATIONS, or (code, a, b) with the two numbers of an
+        activation that has some.  bfloat16 goes to the tcgen05 kernel when TMA can address the operands (K a multiple
         of 8, 16-byte aligned pointers); everything else, and all of float32, to the CUDA cores."""
         self.launches += 1
+        act, act_a, act_b = act if isinstance(act, tuple) else (act, 0.0, 0.0)
         if a.dtype == torch.bfloat16 and self._skinny_ok(M, N, K):
-            if self._skinny(out, a, None, w, bias, act, residual, M, N, K):
+            if self._skinny(out, a, None, w, bias, (act, act_a, act_b), residual, M, N, K):
                 return
         if a.dtype == torch.bfloat16 and self.tensor_cores and K % 8 == 0:
             if CudaOps._lib_split_clusters != bool(self.split_clusters):   # a switch of the library
@@ -493,15 +515,16 @@ class CudaOps:
                 cnt = self._scratch_buffer("tc_counters", need[1], torch.int32)
             code = self.lib.hs_linear_tcgen05(
                 _ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), M, N, K, act,
-                _DT[out.dtype], self.tile_n, self.cta_pairs, _ptr(scratch), _ptr(cnt),
+                act_a, act_b, _DT[out.dtype], self.tile_n, self.cta_pairs, _ptr(scratch), _ptr(cnt),
                 _ptr(self.status),
                 self._stream())
             if code != -1:
                 _check(code, f"linear_tcgen05(M={M},N={N},K={K})")
                 return
         _check(self.lib.hs_linear_simt(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual),
-                                       M, N, K, act, _DT[a.dtype], _DT[out.dtype],
-                                       self._stream()), f"linear(M={M},N={N},K={K})")
+                                       M, N, K, act, act_a, act_b, _DT[a.dtype],
+                                       _DT[out.dtype], self._stream()),
+               f"linear(M={M},N={N},K={K})")
 
     def _skinny_ok(self, M, N, K) -> bool:
         return self.tensor_cores and M <= self.skinny_max_rows
@@ -527,9 +550,10 @@ class CudaOps:
         eps = 0.0
         if norm is not None:
             x, g, b, eps = norm
+        act, act_a, act_b = act if isinstance(act, tuple) else (act, 0.0, 0.0)
         code = self.lib.hs_linear_skinny(
             _ptr(out), _ptr(a), _ptr(x), _ptr(g), _ptr(b), float(eps), _ptr(w), _ptr(bias),
-            _ptr(residual), M, N, K, act, _DT[out.dtype], _ptr(scratch), _ptr(cnt),
+            _ptr(residual), M, N, K, act, act_a, act_b, _DT[out.dtype], _ptr(scratch), _ptr(cnt),
             int(self.pdl), self._stream())
         if code == -1:
             return False
@@ -1018,12 +1042,16 @@ class CudaOps:
                                         stride, n_vec, vec_stride, offset, dims, self._stream()),
                "rotary_pairs")
 
-    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None, w_nk=None):
+    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None, w_nk=None,
+                       exact=False):
         """Block-diagonal linear: ``out[t, g*n + j] = sum_k a[t, a_offset + g*a_group_stride + k]
         * w[g, k, j]``.  ``a`` float32 (a group's input may be a slice of a wider row), ``w``
         [groups, k, n] (k-major), ``out`` [T, groups * n] float32 or of w's type.  ``w_nk`` is
         the same weight as [groups, n, k] in bfloat16: with it, 64 tokens or more and k a
-        multiple of 32, the product runs on the tensor cores (``a`` rounded to bfloat16)."""
+        multiple of 32, the product runs on the tensor cores (``a`` rounded to bfloat16; with
+        ``exact`` ``a`` enters as the sum of three bfloat16 terms, which loses nothing of a
+        float32: for weights that are bfloat16 numbers the result is then the float32 product,
+        and ``out`` is float32)."""
         _want(a, "a", torch.float32, 2)
         _want(w, "w", _FLOATS, 3)
         _want(out, "out", _FLOATS, 2)
@@ -1041,7 +1069,8 @@ class CudaOps:
                 and tuple(w_nk.shape) == (groups, n, k) and w_nk.is_contiguous()):
             code = self.lib.hs_grouped_linear_mma(_ptr(out), _ptr(a), _ptr(w_nk), T, a.shape[1],
                                                   int(a_offset), gs, groups, n, k,
-                                                  _DT[out.dtype], self._stream())
+                                                  _DT[out.dtype], 3 if exact else 1,
+                                                  self._stream())
             if code != -1:
                 _check(code, f"grouped_linear_mma(groups={groups},n={n},k={k})")
                 return
@@ -1537,17 +1566,14 @@ class CudaOps:
         """out = act(z) for an activation with learned numbers ``values``; z float32.
         xielu, values (p, q): z > 0: softplus(p) z^2 + z/2; else (1/2 + softplus(q))
         (e^z - 1 - z) + z/2."""
-        if act != "xielu" or len(values) != LEARNED_ACTIVATIONS["xielu"]:
-            raise KernelError(f"learned_act: activation {act!r} with {len(values)} numbers not taken")
+        a_pos, a_neg = learned_constants(act, values)
         _want(out, "out", _FLOATS)
         _want(z, "z", torch.float32)
         if out.numel() != z.numel():
             raise KernelError("learned_act: sizes differ")
-        sp = lambda v: math.log1p(math.exp(-abs(v))) + max(v, 0.0)      # softplus, in double
         self.launches += 1
-        _check(self.lib.hs_learned_act_xielu(_ptr(out), _ptr(z), z.numel(), sp(values[0]),
-                                             0.5 + sp(values[1]), _DT[out.dtype], self._stream()),
-               "learned_act")
+        _check(self.lib.hs_learned_act_xielu(_ptr(out), _ptr(z), z.numel(), a_pos, a_neg,
+                                             _DT[out.dtype], self._stream()), "learned_act")
 
     def scale_softcap_(self, t, factor, cap):
         """t = cap * tanh(t * factor / cap), in place (float32)."""
@@ -1599,6 +1625,32 @@ class CudaOps:
             int(y_off), int(x_off), _ptr(b_gates), _ptr(rate), _ptr(req_start), _ptr(req_len),
             _ptr(req_slot), req_start.shape[0], C, int(blocks), int(taps), float(decay_scale),
             _DT[out.dtype], self._stream()), f"rglru_scan(channels={C})")
+
+    def rglru_step(self, out, state, proj, conv_w, conv_b, w_gates, b_gates, rate, tok_req,
+                   req_slot, *, channels, blocks, taps, decay_scale, y_off, x_off) -> bool:
+        """``rglru_conv``, the gates' block-diagonal product and ``rglru_scan`` for a step in
+        which every request brings ONE token, in one launch and with the same bits.
+        ``w_gates`` float32 [blocks, n, 2n].  False (nothing done) for parts of the channels
+        too large for its shared memory."""
+        for name, v in (("proj", proj), ("state", state)):
+            _want(v, name, torch.float32, 2)
+        _want(out, "out", _FLOATS, 2)
+        _want(w_gates, "w_gates", torch.float32, 3)
+        C, n = int(channels), int(channels) // int(blocks)
+        if out.shape[1] != C or tuple(w_gates.shape) != (blocks, n, 2 * n) or rate.shape[0] != C \
+                or b_gates.shape[0] != 2 * C or state.shape[1] < C * taps \
+                or max(y_off, x_off) + C > proj.shape[1] or conv_w.shape != (C, taps):
+            raise KernelError("rglru_step: shapes do not fit")
+        code = self.lib.hs_rglru_step(
+            _ptr(out), _ptr(state), state.shape[1], _ptr(proj), proj.shape[1], int(y_off),
+            int(x_off), _ptr(conv_w), _ptr(conv_b), _ptr(w_gates), _ptr(b_gates), _ptr(rate),
+            _ptr(tok_req), _ptr(req_slot), out.shape[0], C, int(blocks), int(taps),
+            float(decay_scale), _DT[out.dtype], self._stream())
+        if code == -1:
+            return False
+        _check(code, f"rglru_step(channels={C})")
+        self.launches += 1
+        return True
 
     # -- attention over a window and pooled blocks --------------------------------------------
     def pooled_prepare(self, q_out, pool, proj, wq, wk, freq_qk, freq_v, table, tok_pos, tok_req,

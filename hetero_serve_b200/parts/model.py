@@ -147,7 +147,9 @@ class SandwichNormBlock(Block):
     A sublayer's output goes to a float32 block of its own (as under ``output_norm``); the norm
     behind it is added into the stream by ``add_normed``, which in the same launch forms the
     rows of the norm in front of the feed-forward.  A layer may leave ``norm2``,
-    ``feed_forward`` and ``norm2b`` out (all or none): it then ends after the mixer."""
+    ``feed_forward`` and ``norm2b`` out (all or none): it then ends after the mixer.  When the
+    block that runs next is of this arrangement too, the layer's last launch also forms the
+    rows of THAT block's first norm (``ctx.normed_ahead``), which then skips it."""
 
     slots = {"norm1": "norm", "mixer": "mixer", "norm1b": "norm", "norm2": "norm",
              "feed_forward": "feed_forward", "norm2b": "norm"}
@@ -170,14 +172,18 @@ class SandwichNormBlock(Block):
         T, W = x.shape
         h = ctx.buffer("normed", (T, W), ctx.dtype)
         y = ctx.buffer("sublayer_out", (T, W), torch.float32)
-        self.norm1.forward(ctx, h, x)
+        if not getattr(ctx, "normed_ahead", False):
+            self.norm1.forward(ctx, h, x)
+        nxt = getattr(ctx, "next_block", None)
+        ahead = (nxt.norm1, h) if isinstance(nxt, SandwichNormBlock) else None
+        ctx.normed_ahead = ahead is not None
         out = OutputNormBlock._run(self.mixer, ctx, h, y, cache)
         if not self.has_ff:
-            self.norm1b.add_normed(ctx, x, out)
+            self.norm1b.add_normed(ctx, x, out, then=ahead)
             return
         self.norm1b.add_normed(ctx, x, out, then=(self.norm2, h))
         out = OutputNormBlock._run(self.feed_forward, ctx, h, y)
-        self.norm2b.add_normed(ctx, x, out)
+        self.norm2b.add_normed(ctx, x, out, then=ahead)
 
 
 _ARRANGEMENTS: dict[str, Callable[[LayerSpec], Block]] = {"pre_norm": PreNormBlock,
@@ -331,10 +337,13 @@ class Model:
         ctx.position = self.position          # mixers ask it whether it acts on queries and keys
         self.embedding.forward(ctx, x, self.position)
         ctx.stream_copy_fresh = False         # no copy of the stream in the compute type yet
+        ctx.normed_ahead = False              # nobody has formed the next block's first norm
         for idx, call in enumerate(self.schedule):
             ctx.call_index = idx
             cache = ctx.cache_view(call) if call.cache in self.entry_location else None
             block = self.blocks[call.layer]
+            ctx.next_block = (self.blocks[self.schedule[idx + 1].layer]
+                              if idx + 1 < len(self.schedule) else None)
             block.forward(ctx, x, cache)
             if not getattr(block, "keeps_stream_copy", False):
                 ctx.stream_copy_fresh = False

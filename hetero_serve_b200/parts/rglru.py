@@ -58,6 +58,14 @@ class RealGatedRecurrence(Mixer):
         self.w_gates = torch.cat([t[p + "ra"].transpose(1, 2), t[p + "ri"].transpose(1, 2)],
                                  dim=2).contiguous()
         self.b_gates = torch.cat([t[p + "ra.b"], t[p + "ri.b"]], dim=1).reshape(-1).contiguous()
+        # gate matrices that are bfloat16 numbers (a checkpoint stored in bfloat16): prompt
+        # portions of a bfloat16 engine form the gates on the tensor cores, the float32 input
+        # entering as three bfloat16 terms, which is the float32 product
+        self.w_gates_nk = None
+        if self.w_in.dtype == torch.bfloat16:
+            nk = self.w_gates.transpose(1, 2).contiguous()
+            if bool((nk.bfloat16().float() == nk).all()):
+                self.w_gates_nk = nk.bfloat16()
         self.rate = torch.nn.functional.softplus(t[p + "lam"].double()).float().contiguous()
         self.w_out = t[p + "o"]
 
@@ -70,12 +78,22 @@ class RealGatedRecurrence(Mixer):
         proj = ctx.buffer("rglru_proj", (T, 2 * C), f32)
         ops.linear(proj, h, self.w_in, self.b_in)
         state = ctx.state()
+        mixed = ctx.buffer("rglru_mixed", (T, C), ctx.dtype)
+        plan = getattr(ctx, "plan", None)
+        step = getattr(ops, "rglru_step", None)
+        if (step is not None and plan is not None and plan.single_new and plan.tile_cap == 0
+                and step(mixed, state, proj, self.conv_w, self.conv_b, self.w_gates,
+                         self.b_gates, self.rate, ctx.tok_req, ctx.req_slot, channels=C,
+                         blocks=self.B, taps=self.taps, decay_scale=self.decay_scale, y_off=0,
+                         x_off=C)):
+            # every request brings one token: convolution, gates and the state's step at once
+            ops.linear(x, mixed, self.w_out, None, residual=None if fresh else x)
+            return
         u = ctx.buffer("rglru_u", (T, C), f32)
         ops.rglru_conv(u, proj, self.conv_w, self.conv_b, state, ctx.tok_req, ctx.req_start,
                        ctx.req_slot, x_off=C, channels=C, taps=self.taps)
         z = ctx.buffer("rglru_gates", (T, 2 * C), f32)
-        ops.grouped_linear(z, u, self.w_gates)
-        mixed = ctx.buffer("rglru_mixed", (T, C), ctx.dtype)
+        ops.grouped_linear(z, u, self.w_gates, w_nk=self.w_gates_nk, exact=True)
         ops.rglru_scan(mixed, state, u, z, proj, self.b_gates, self.rate, ctx.req_start,
                        ctx.req_len, ctx.req_slot, channels=C, blocks=self.B, taps=self.taps,
                        decay_scale=self.decay_scale, y_off=0, x_off=C)

@@ -254,14 +254,14 @@ class DenseFeedForward(FeedForward):
     def forward(self, ctx, h, x, norm=None, fresh=False):
         T = h.shape[0]
         u = ctx.buffer("ff_inner", (T, self.inner), ctx.dtype)
-        if self.act_name:
-            # the product leaves float32 numbers; the activation reads them and writes the
-            # rows the second product takes
+        if self.act_name and norm is None:
+            # an activation with learned numbers, on the float32 sums of the product
+            ctx.ops.linear(u, h, self.w_in, self.b_in, act=self.act, act_values=self.act_values)
+        elif self.act_name:
+            # behind a norm that is fused into the product: the product leaves float32
+            # numbers, the activation reads them and writes the rows the second product takes
             z = ctx.buffer("ff_inner_f32", (T, self.inner), torch.float32)
-            if norm is not None:
-                norm.linear(ctx, z, h, x, self.w_in, self.b_in)
-            else:
-                ctx.ops.linear(z, h, self.w_in, self.b_in)
+            norm.linear(ctx, z, h, x, self.w_in, self.b_in)
             ctx.ops.learned_act(u, z, self.act, self.act_values)
         elif norm is not None:
             norm.linear(ctx, u, h, x, self.w_in, self.b_in, act=self.act)

@@ -52,11 +52,16 @@ class PlainOps:
         var = (c * c).mean(-1, keepdim=True)
         out.copy_((c / torch.sqrt(var + eps) * gamma.to(self.cd) + beta.to(self.cd)).to(out.dtype))
 
-    def linear(self, out, a, w, bias=None, act="none", residual=None):
+    def linear(self, out, a, w, bias=None, act="none", residual=None, act_values=()):
         v = a.to(self.cd) @ w.to(self.cd).T
         if bias is not None:
             v = v + bias.to(self.cd)
-        v = _ACT[act](v)
+        if act_values:
+            tmp = torch.empty_like(v)
+            self.learned_act(tmp, v, act, act_values)
+            v = tmp
+        else:
+            v = _ACT[act](v)
         if residual is not None:
             v = v + residual.to(self.cd)
         out.copy_(v.to(out.dtype))
@@ -154,7 +159,7 @@ class PlainOps:
                 seg[1::2] = b * c + a * s
                 buf[t, lo:lo + dims] = seg.to(buf.dtype)
 
-    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None, w_nk=None):
+    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None, w_nk=None, exact=False):
         groups, k, n = w.shape
         gs = k if a_group_stride is None else a_group_stride
         T = out.shape[0]
@@ -573,7 +578,7 @@ class PlainOps:
 
     def pooled_attention(self, out, q, pool, table, coarse_pool, coarse_table, tok_pos, tok_req,
                          freq_v, *, n_heads, n_kv_heads, head_dim, value_dim, window, block,
-                         scale, page_size, status):
+                         scale, page_size, status, plan=None):
         H, G, D, V = n_heads, n_kv_heads, head_dim, value_dim
         fine = pool.view(-1, G, page_size, D + V)
         coarse = coarse_pool.view(-1, G, page_size, D + V)

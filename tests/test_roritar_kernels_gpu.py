@@ -72,6 +72,28 @@ def test_learned_activation(ops, dtype, tol):
         close(out, want, tol)
 
 
+@pytest.mark.parametrize("dtype, M, K, tol", [(F32, 5, 64, 2e-5), (F32, 40, 64, 2e-5), (F32, 300, 66, 2e-5),
+                                              (BF16, 3, 64, 4e-2), (BF16, 40, 64, 4e-2),
+                                              (BF16, 300, 64, 4e-2), (BF16, 700, 2048, 4e-2)])
+def test_learned_activation_behind_a_product(ops, dtype, M, K, tol):
+    """The activation as the last step of every linear kernel (few rows, tiles on the CUDA
+    cores, tcgen05 with and without a split over the summed index): applied to the float32
+    sums, before a residual, with numbers of either sign."""
+    for values in ((0.8, -0.3), (-1.5, 2.0)):
+        a, w = rnd(M, K, seed=1).to(dtype), rnd(96, K, seed=2, std=2.0 / math.sqrt(K)).to(dtype)
+        bias, res = rnd(96, seed=3), rnd(M, 96, seed=4)
+        p, q = (torch.tensor(v, dtype=F64) for v in values)
+        z = a.double() @ w.double().T
+        got = torch.zeros(M, 96, dtype=F32, device=DEV)
+        ops.linear(got, dev(a), dev(w), dev(bias), act="xielu", residual=dev(res), act_values=values)
+        close(got, P.xielu(z + bias.double(), p, q) + res.double(), tol)
+        got2 = torch.zeros(M, 96, dtype=dtype, device=DEV)
+        ops.linear(got2, dev(a), dev(w), None, act="xielu", act_values=values)
+        close(got2, P.xielu(z, p, q), tol if dtype == F32 else 8e-2)
+    with pytest.raises(Exception):
+        ops.linear(got2, dev(a), dev(w), None, act="xielu", act_values=(1.0,))
+
+
 def test_scaled_and_capped_logits(ops):
     z = rnd(5, 777, seed=6, std=40.0)
     for s, cap in ((0.25, 15.0), (1.0, 30.0), (3.0, 0.5)):
@@ -143,6 +165,44 @@ def test_recurrence_in_portions_and_batches(ops, dtype, tol, C, B, taps):
     assert fed == {r: h.shape[0] for r, h in rows.items()}
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("C, B, taps", [(40, 2, 4), (36, 3, 3), (24, 1, 1), (256, 4, 4), (70, 7, 2),
+                                        (1024, 2, 4), (2400, 1, 2)])
+def test_single_tokens_in_one_launch(ops, dtype, C, B, taps):
+    """A step in which every request brings one token: convolution, gates and the state's step
+    in one launch give the bits of the three launches (outputs, states and the convolution's
+    history), step after step, in slots that are in no order and beside a row of padding."""
+    w = _recurrence_weights(C, B, taps, 50)
+    w_gates = dev(torch.cat([w["m.ra"].transpose(1, 2), w["m.ri"].transpose(1, 2)], 2))
+    b_gates = dev(torch.cat([w["m.ra.b"], w["m.ri.b"]], 1).reshape(-1))
+    rate = dev(torch.nn.functional.softplus(w["m.lam"].double()).float())
+    cw, cb = dev(w["m.conv"]), dev(w["m.conv.b"])
+    state_a = torch.zeros(5, C * taps, device=DEV)
+    state_b = torch.zeros(5, C * taps, device=DEV)
+    tok_req, req_slot = ints([0, 1, 2, -1]), ints([4, 0, 2])
+    req_start, req_len = ints([0, 1, 2]), ints([1, 1, 1])
+    kw = dict(channels=C, blocks=B, taps=taps, decay_scale=8.0, y_off=0, x_off=C)
+    for i in range(9):
+        proj = dev(rnd(4, 2 * C, seed=60 + i))
+        u = torch.zeros(4, C, device=DEV)
+        ops.rglru_conv(u, proj, cw, cb, state_a, tok_req, req_start, req_slot, x_off=C,
+                       channels=C, taps=taps)
+        z = torch.zeros(4, 2 * C, device=DEV)
+        ops.grouped_linear(z, u, w_gates)
+        want = torch.zeros(4, C, dtype=dtype, device=DEV)
+        ops.rglru_scan(want, state_a, u, z, proj, b_gates, rate, req_start, req_len, req_slot, **kw)
+        got = torch.zeros(4, C, dtype=dtype, device=DEV)
+        before = ops.launches
+        took = ops.rglru_step(got, state_b, proj, cw, cb, w_gates, b_gates, rate, tok_req,
+                              req_slot, **kw)
+        if C // B * 9 * 4 > 40 * 1024:
+            assert not took and ops.launches == before       # a part too large: refused
+            return
+        assert took and ops.launches == before + 1
+        assert torch.equal(got, want) and torch.equal(state_a, state_b), i
+    assert float(state_b[4, :C].abs().max()) > 0 and float(state_b[1].abs().max()) == 0
+
+
 def test_recurrence_keeps_a_long_memory(ops):
     """A decay close to 1: sqrt(1 - a^2) must keep its digits, and the state of the first token
     still counts after hundreds of steps taken one at a time."""
@@ -170,6 +230,32 @@ def test_recurrence_keeps_a_long_memory(ops):
         if t % 50 == 49 or t < 3:
             close(out[0], want[t], 2e-5)
     assert float(want[399].abs().max()) > 1.0                  # the first input is still there
+
+
+@pytest.mark.parametrize("T, groups, k, n", [(64, 1, 32, 32), (200, 4, 64, 128), (1000, 3, 96, 40)])
+def test_block_diagonal_product_in_three_terms(ops, T, groups, k, n):
+    """With weights that are bfloat16 numbers, the tensor-core product of a float32 input that
+    enters as three bfloat16 terms is the float32 product: it is compared with the float64
+    product at float32's resolution, where the one-term product is a hundred times further
+    off.  The inputs span six orders of magnitude."""
+    a = rnd(T, groups * k, seed=71) * torch.logspace(-3, 3, groups * k)
+    w = rnd(groups, k, n, seed=72).to(BF16).float()
+    want = torch.einsum("tgk,gkn->tgn", a.double().view(T, groups, k), w.double()).reshape(T, -1)
+    size = torch.einsum("tgk,gkn->tgn", a.double().abs().view(T, groups, k),
+                        w.double().abs()).reshape(T, -1)
+    w_nk = dev(w.transpose(1, 2).contiguous().to(BF16))
+    got = torch.full((T, groups * n), float("nan"), device=DEV)
+    before = ops.launches
+    ops.grouped_linear(got, dev(a), dev(w), w_nk=w_nk, exact=True)
+    assert ops.launches == before + 1
+    err = ((got.cpu().double() - want).abs() / size).max().item()
+    assert err < 3e-7, err
+    rough = torch.zeros(T, groups * n, device=DEV)
+    ops.grouped_linear(rough, dev(a), dev(w), w_nk=w_nk)
+    assert ((rough.cpu().double() - want).abs() / size).max().item() > 30 * err
+    plain = torch.zeros(T, groups * n, device=DEV)
+    ops.grouped_linear(plain, dev(a), dev(w))                 # the CUDA-core kernel
+    assert ((plain.cpu().double() - want).abs() / size).max().item() < 3e-7
 
 
 # -- attention over a window and pooled blocks ------------------------------------------------------
