@@ -39,7 +39,8 @@ pooled_prepare_kernel(float* __restrict__ q_out, TC* __restrict__ pool,
                       const int* __restrict__ table, int max_pages, int num_pages,
                       const int* __restrict__ tok_pos, const int* __restrict__ tok_req,
                       int H, int G, int D, int V, int rot_dims, float eps, int page_size,
-                      int writes, int* __restrict__ status) {
+                      int writes, TC* __restrict__ coarse, const int* __restrict__ ctable,
+                      int cmax_pages, int cnum_pages, int block, int* __restrict__ status) {
   extern __shared__ float s_vec[];                 // [PA_WARPS][max(D, V)]
   pdl_trigger();
   pdl_wait();
@@ -100,6 +101,37 @@ pooled_prepare_kernel(float* __restrict__ q_out, TC* __restrict__ pool,
       if (cdst) cdst[e] = from_f<TC>(own);
     }
     __syncwarp();
+  }
+  // With the companion pool (handed in only when every request brings ONE token, so that the
+  // other rows of a block are of earlier steps): a token that completes a block forms the
+  // block's mean row here, summed as pooled_means sums it.
+  if (coarse == nullptr || row == nullptr || (pos + 1) % block) return;
+  __syncthreads();                                 // this token's row is in its page
+  const int b = pos / block;
+  const int cpi = b / page_size;
+  const int cpage = cpi < cmax_pages ? ctable[(size_t)r * cmax_pages + cpi] : -1;
+  if (cpage < 0 || cpage >= cnum_pages) {
+    if (threadIdx.x == 0) atomicOr(status, HS_STATUS_BAD_PAGE);
+    return;
+  }
+  const int row_len = D + V;
+  const float inv = 1.0f / (float)block;
+  for (int idx = threadIdx.x; idx < G * row_len; idx += blockDim.x) {
+    const int g = idx / row_len, e = idx - g * row_len;
+    float acc = 0.f;
+    bool ok = true;
+    for (int j = b * block; j <= pos; ++j) {
+      const int pi = j / page_size;
+      const int page = pi < max_pages ? table[(size_t)r * max_pages + pi] : -1;
+      if (page < 0 || page >= num_pages) { ok = false; break; }
+      acc += to_f(pool[(((size_t)page * G + g) * page_size + (j % page_size)) * (size_t)row_len + e]);
+    }
+    if (!ok) {
+      atomicOr(status, HS_STATUS_BAD_PAGE);
+      continue;
+    }
+    coarse[(((size_t)cpage * G + g) * page_size + (b % page_size)) * (size_t)row_len + e] =
+        from_f<TC>(acc * inv);
   }
 }
 
@@ -295,10 +327,12 @@ HS_EXPORT int hs_pooled_prepare(float* q_out, void* pool, const float* proj, int
                                 const float* freq_v, const int* table, int max_pages,
                                 int num_pages, const int* tok_pos, const int* tok_req,
                                 int n_tokens, int H, int G, int D, int V, int rot_dims, float eps,
-                                int page_size, int writes, int cache_dtype, int* status,
-                                void* stream) {
+                                int page_size, int writes, int cache_dtype, void* coarse,
+                                const int* ctable, int cmax_pages, int cnum_pages, int block,
+                                int* status, void* stream) {
   if (!q_out || !pool || !proj || !table || !tok_pos || !tok_req || !status)
     return HS_ERR_ARGUMENT;
+  if (coarse && (!ctable || block <= 0 || cmax_pages <= 0 || !writes)) return HS_ERR_ARGUMENT;
   if ((wq == nullptr) != (wk == nullptr) || (rot_dims > 0 && !freq_qk)) return HS_ERR_ARGUMENT;
   if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0 || rot_dims < 0 || rot_dims % 2 ||
       rot_dims > D || (freq_v && V % 2) || page_size <= 0)
@@ -313,12 +347,13 @@ HS_EXPORT int hs_pooled_prepare(float* q_out, void* pool, const float* proj, int
                   dim3(hs::PA_WARPS * 32), smem, st, hs_pdl_enabled(), q_out,
                   (__nv_bfloat16*)pool, proj, proj_stride, wq, wk, freq_qk, freq_v, table,
                   max_pages, num_pages, tok_pos, tok_req, H, G, D, V, rot_dims, eps, page_size,
-                  writes, status);
+                  writes, (__nv_bfloat16*)coarse, ctable, cmax_pages, cnum_pages, block, status);
   else if (cache_dtype == HS_DT_F32)
     e = hs_launch(hs::pooled_prepare_kernel<float>, dim3(n_tokens), dim3(hs::PA_WARPS * 32), smem,
                   st, hs_pdl_enabled(), q_out, (float*)pool, proj, proj_stride, wq, wk, freq_qk,
                   freq_v, table, max_pages, num_pages, tok_pos, tok_req, H, G, D, V, rot_dims,
-                  eps, page_size, writes, status);
+                  eps, page_size, writes, (float*)coarse, ctable, cmax_pages, cnum_pages, block,
+                  status);
   else
     return HS_ERR_UNSUPPORTED;
   return e == cudaSuccess ? HS_OK : (int)e;

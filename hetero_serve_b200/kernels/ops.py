@@ -230,7 +230,7 @@ def _declare(lib) -> None:
         "hs_rglru_scan": [P, P, I, P, P, P, I, I, I, P, P, P, P, P, I, I, I, I, F, I, P],
         "hs_rglru_step": [P, P, I, P, I, I, I, P, P, P, P, P, P, P, I, I, I, I, F, I, P],
         "hs_pooled_prepare": [P, P, P, I, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, I, I,
-                              I, P, P],
+                              I, P, P, I, I, I, P, P],
         "hs_pooled_means": [P, P, I, I, P, P, I, I, P, P, I, I, I, I, I, I, P, P],
         "hs_pooled_attention": [P, P, P, P, I, I, P, P, I, I, P, P, P, I, I, I, I, I, I, I, F, I,
                                 I, I, P, P, P, P],
@@ -326,6 +326,7 @@ class CudaOps:
         self.latent_mma = True      # prompt portions of latent attention on the tensor cores
         self.biased_mma = True      # prompt portions of the biased chunk attention likewise
         self.pooled_mma = True      # ... and of the attention over a window and pooled blocks
+        self.folds_pooled_means = True   # pooled_prepare takes the companion pool (single tokens)
         self.lightning_bulk_rows = 64   # from this many tokens a step on, lightning attention
         #                                 activates its rows in a pass of their own
         self.latent_splits = None   # blocks a token's keys are split over in latent attention
@@ -1655,7 +1656,7 @@ class CudaOps:
     # -- attention over a window and pooled blocks --------------------------------------------
     def pooled_prepare(self, q_out, pool, proj, wq, wk, freq_qk, freq_v, table, tok_pos, tok_req,
                        *, n_heads, n_kv_heads, head_dim, value_dim, rot_dims, eps, writes,
-                       page_size, status):
+                       page_size, status, coarse_pool=None, coarse_table=None, block=0):
         """From the float32 rows [q | k | v] of ``proj``: per-head RMS norms of q and k
         (weights ``wq``, ``wk`` or None), rotation of their first ``rot_dims`` numbers by the
         position (pairs d, d + rot_dims/2), rotation of the values over all of value_dim
@@ -1669,12 +1670,20 @@ class CudaOps:
         if q_out.shape[1] != H * D or proj.shape[1] < (H + G) * D + G * V:
             raise KernelError("pooled_prepare: the rows do not fit the heads")
         num_pages = pool.numel() // (G * page_size * (D + V))
+        cmax = cnum = 0
+        if coarse_pool is not None:
+            # only for steps in which every request brings ONE token: a token that completes a
+            # block then forms the block's mean row here (``pooled_means`` is not needed)
+            _want(coarse_pool, "coarse_pool", pool.dtype)
+            _want(coarse_table, "coarse_table", torch.int32, 2)
+            cmax, cnum = coarse_table.shape[1], coarse_pool.numel() // (G * page_size * (D + V))
         self.launches += 1
         _check(self.lib.hs_pooled_prepare(
             _ptr(q_out), _ptr(pool), _ptr(proj), proj.shape[1], _ptr(wq), _ptr(wk),
             _ptr(freq_qk), _ptr(freq_v), _ptr(table), table.shape[1], num_pages, _ptr(tok_pos),
             _ptr(tok_req), q_out.shape[0], H, G, D, V, int(rot_dims), float(eps), int(page_size),
-            int(bool(writes)), _DT[pool.dtype], _ptr(status), self._stream()),
+            int(bool(writes)), _DT[pool.dtype], _ptr(coarse_pool), _ptr(coarse_table), cmax, cnum,
+            int(block), _ptr(status), self._stream()),
             f"pooled_prepare(head_dim={D},value_dim={V})")
 
     def pooled_means(self, coarse_pool, coarse_table, pool, table, tok_pos, tok_req, *,

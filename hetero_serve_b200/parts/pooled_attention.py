@@ -92,18 +92,24 @@ class PooledWindowAttention(Mixer):
         sizes = dict(n_heads=self.H, n_kv_heads=self.G, head_dim=self.D, value_dim=self.V,
                      page_size=cache.page_size, status=ctx.status)
         coarse = cache.coarse
+        plan = getattr(ctx, "plan", None)
+        # every request brings one token: the rows of a block that is completed now are of
+        # earlier steps, and the launch that appends forms the block's mean as well
+        folded = (cache.writes and plan is not None and plan.single_new and plan.tile_cap == 0
+                  and getattr(ops, "folds_pooled_means", False))
+        extra = dict(coarse_pool=coarse.pool, coarse_table=coarse.table, block=self.pool) \
+            if folded else {}
         ops.pooled_prepare(q, cache.pool, proj, self.w_qn, self.w_kn, self.freq_qk, self.freq_v,
                            cache.table, ctx.tok_pos, ctx.tok_req, rot_dims=self.rot_dims,
-                           eps=self.eps, writes=cache.writes, **sizes)
-        if cache.writes:
+                           eps=self.eps, writes=cache.writes, **sizes, **extra)
+        if cache.writes and not folded:
             ops.pooled_means(coarse.pool, coarse.table, cache.pool, cache.table, ctx.tok_pos,
                              ctx.tok_req, n_kv_heads=self.G, row=self.D + self.V,
                              block=self.pool, page_size=cache.page_size, status=ctx.status)
         att = ctx.buffer("pooled_att", (T, self.H * self.V), ctx.dtype)
         ops.pooled_attention(att, q, cache.pool, cache.table, coarse.pool, coarse.table,
                              ctx.tok_pos, ctx.tok_req, self.freq_v, window=self.window,
-                             block=self.pool, scale=self.scale,
-                             plan=getattr(ctx, "plan", None), **sizes)
+                             block=self.pool, scale=self.scale, plan=plan, **sizes)
         ops.linear(x, att, self.w_out, None, residual=None if fresh else x)
 
 

@@ -309,7 +309,7 @@ def test_pooled_window_attention(ops, dtype, tol, H, G, D, V, window, pool, rot,
     fv = dev(_frequencies(300.0, V))
     wq, wk = dev(w["m.q.norm"], w["m.k.norm"])
     plan = [[("a", 37)], [("a", 2), ("b", 30)], [("b", 1), ("a", 58)], [("a", 1), ("b", 1)],
-            [("b", 45), ("a", 1)], [("a", 1)], [("a", 50)]]
+            [("b", 45), ("a", 1)], [("a", 1)]] + [[("a", 1)]] * 17 + [[("a", 33)]]
     fed = {"a": 0, "b": 0}
     idx = {"a": 0, "b": 1}
     for step in plan:
@@ -321,13 +321,17 @@ def test_pooled_window_attention(ops, dtype, tol, H, G, D, V, window, pool, rot,
         tab, ctab = table[order].contiguous(), ctable[order].contiguous()
         q = torch.zeros(T, H * D, device=DEV)
         sizes = dict(n_heads=H, n_kv_heads=G, head_dim=D, value_dim=V, page_size=page, status=status)
+        # single tokens only: the launch that appends also forms the mean of a block it completes
+        folded = planned and all(k == 1 for _, k in step)
+        extra = dict(coarse_pool=coarse, coarse_table=ctab, block=pool) if folded else {}
         ops.pooled_prepare(q, fine, proj, wq, wk, fq, fv, tab, tok_pos, tok_req, rot_dims=rot,
-                           eps=eps, writes=True, **sizes)
+                           eps=eps, writes=True, **sizes, **extra)
         for row, (r, k) in enumerate(step):
             lo = max(0, min(fed[r] - window + 1, fed[r] // pool * pool))
             tab[row, :lo // page] = -1
-        ops.pooled_means(coarse, ctab, fine, tab, tok_pos, tok_req, n_kv_heads=G, row=D + V,
-                         block=pool, page_size=page, status=status)
+        if not folded:
+            ops.pooled_means(coarse, ctab, fine, tab, tok_pos, tok_req, n_kv_heads=G, row=D + V,
+                             block=pool, page_size=page, status=status)
         out = torch.full((T, H * V), float("nan"), dtype=dtype, device=DEV)
         work = ops.make_plan([(row, row, fed[r], k) for row, (r, k) in enumerate(step)], T, page) \
             if planned else None
