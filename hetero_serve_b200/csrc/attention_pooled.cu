@@ -213,7 +213,11 @@ __device__ __forceinline__ float dot_row(const __nv_bfloat16* __restrict__ k, co
   return s;
 }
 
-// PA_MAXC: value columns a lane owns (V <= 32 * PA_MAXC); the launcher picks 2, 8 or 32
+// PA_MAXC: value columns a lane owns (V <= 32 * PA_MAXC); the launcher picks 2, 8 or 32.
+// A block serves one (token, head).  Its warps take rounds of 32 keys in turn (warp w the rounds
+// w, w + PA_WARPS, ...), each with a running maximum, sum and output of its own, and the block
+// joins them at the end: a single token's keys are walked by eight warps side by side instead of
+// one after the other.  How the keys are dealt depends on the token's own position only.
 template <typename TC, typename TO, int PA_MAXC>
 __global__ void __launch_bounds__(PA_WARPS * 32)
 pooled_attention_kernel(TO* __restrict__ out, const float* __restrict__ q,
@@ -225,26 +229,27 @@ pooled_attention_kernel(TO* __restrict__ out, const float* __restrict__ q,
                         int V, int window, int block, float scale, int page_size, int vec,
                         const int* __restrict__ listed, const int* __restrict__ plan_head,
                         int* __restrict__ status) {
-  extern __shared__ float s_q[];                   // [PA_WARPS][max(D, V)]
+  extern __shared__ float s_pa[];                  // q [D] | acc [PA_WARPS][V] | m, l [2 PA_WARPS]
+  float* sq = s_pa;
+  float* s_acc = s_pa + D;
+  float* s_ml = s_acc + (size_t)PA_WARPS * V;
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // consecutive tokens of one head share a block: their windows overlap in the L1
-  const long long item = (long long)blockIdx.x * PA_WARPS + warp;
+  const long long item = blockIdx.x;
   // with a list only the listed tokens are served, as many as the list's head says
   const int n_here = listed ? min(n_tokens, plan_head[0]) : n_tokens;
   if (item >= (long long)n_here * H) return;
+  // consecutive tokens of one head are neighbours in the grid: their windows overlap in the L2
   const int h = (int)(item / n_here), entry = (int)(item - (long long)h * n_here);
   const int t = listed ? listed[3 * entry] : entry;
   const int r = tok_req[t];
   if (r < 0) return;
   const int pos = tok_pos[t];
   const int g = h / (H / G);
-  const int ext = max(D, V);
-  float* sq = s_q + (size_t)warp * ext;
   const float* qr = q + (size_t)t * H * D + (size_t)h * D;
-  for (int e = lane; e < D; e += 32) sq[e] = qr[e] * scale;
-  __syncwarp();
+  for (int e = threadIdx.x; e < D; e += PA_WARPS * 32) sq[e] = qr[e] * scale;
+  __syncthreads();
   const int row_len = D + V;
   const int first = max(0, pos - window + 1);
   const int seen = max(0, (pos - window + 1) / block);    // blocks wholly behind the window
@@ -256,7 +261,7 @@ pooled_attention_kernel(TO* __restrict__ out, const float* __restrict__ q,
 #pragma unroll
   for (int c = 0; c < PA_MAXC; ++c) acc[c] = 0.f;
   bool bad = false;
-  for (int base = 0; base < n_keys; base += 32) {
+  for (int base = warp * 32; base < n_keys; base += PA_WARPS * 32) {
     const int kk = base + lane;
     const TC* krow = nullptr;
     if (kk < n_keys) {
@@ -282,36 +287,71 @@ pooled_attention_kernel(TO* __restrict__ out, const float* __restrict__ q,
     m = m_new;
 #pragma unroll
     for (int c = 0; c < PA_MAXC; ++c) acc[c] *= corr;
-    const int n_here = min(32, n_keys - base);
-    for (int jj = 0; jj < n_here; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const unsigned long long ptr =
-          __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)krow, jj);
-      if (ptr == 0ull) continue;
-      const TC* vrow = reinterpret_cast<const TC*>((uintptr_t)ptr) + D;
+    const int n_round = min(32, n_keys - base);
+    // four value rows in flight: their loads are issued before the first is used
+    for (int jj = 0; jj < n_round; jj += 4) {
+      float pj[4];
+      const TC* vr[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int src = (jj + u) & 31;
+        pj[u] = __shfl_sync(0xffffffffu, p, src);
+        const unsigned long long ptr =
+            __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)krow, src);
+        vr[u] = jj + u < n_round && ptr != 0ull ? reinterpret_cast<const TC*>((uintptr_t)ptr) + D
+                                                : nullptr;
+      }
 #pragma unroll
       for (int c = 0; c < PA_MAXC; ++c) {
         const int e = c * 32 + lane;
-        if (e < V) acc[c] = fmaf(pj, to_f(vrow[e]), acc[c]);
+        if (e < V) {
+          float v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] = vr[u] ? to_f(vr[u][e]) : 0.f;
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (vr[u]) acc[c] = fmaf(pj[u], v[u], acc[c]);
+        }
       }
     }
   }
   if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(status, HS_STATUS_BAD_PAGE);
-  // the head's output, turned back by the query's position (pairs e, e + V/2)
-  __syncwarp();
-  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  // the warps' shares joined under one maximum, in the order of the warps
+  if (lane == 0) {
+    s_ml[warp] = m;
+    s_ml[PA_WARPS + warp] = l;
+  }
 #pragma unroll
   for (int c = 0; c < PA_MAXC; ++c) {
     const int e = c * 32 + lane;
-    if (e < V) sq[e] = acc[c] * inv;
+    if (e < V) s_acc[(size_t)warp * V + e] = acc[c];
   }
-  __syncwarp();
+  __syncthreads();
+  float top = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < PA_WARPS; ++w) top = fmaxf(top, s_ml[w]);
+  float total = 0.f, share[PA_WARPS];
+#pragma unroll
+  for (int w = 0; w < PA_WARPS; ++w) {
+    share[w] = s_ml[w] == -INFINITY ? 0.f : expf(s_ml[w] - top);
+    total = fmaf(s_ml[PA_WARPS + w], share[w], total);
+  }
+  const float inv = total > 0.f ? 1.0f / total : 0.f;
+  __syncthreads();
+  for (int e = threadIdx.x; e < V; e += PA_WARPS * 32) {
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < PA_WARPS; ++w) o = fmaf(s_acc[(size_t)w * V + e], share[w], o);
+    s_acc[e] = o * inv;                            // row 0 of the shares: each thread its own e
+  }
+  __syncthreads();
+  // the head's output, turned back by the query's position (pairs e, e + V/2)
   TO* orow = out + (size_t)t * H * V + (size_t)h * V;
   const int half = V >> 1;
-  for (int e = lane; e < V; e += 32) {
-    float own = sq[e];
+  for (int e = threadIdx.x; e < V; e += PA_WARPS * 32) {
+    float own = s_acc[e];
     if (freq_v != nullptr) {
-      const float partner = sq[e < half ? e + half : e - half];
+      const float partner = s_acc[e < half ? e + half : e - half];
       float c, s;
       pair_angle(pos, freq_v[e < half ? e : e - half], &c, &s);
       own = e < half ? own * c + partner * s : own * c - partner * s;      // the angle negated
@@ -401,10 +441,11 @@ HS_EXPORT int hs_pooled_attention(void* out, const float* q, const void* pool, c
       block <= 0 || page_size <= 0 || (freq_v && V % 2))
     return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
-  const size_t smem = (size_t)hs::PA_WARPS * (D > V ? D : V) * sizeof(float);
+  const size_t smem = ((size_t)D + (size_t)hs::PA_WARPS * (V + 2)) * sizeof(float);
   if (smem > 48 * 1024) return HS_ERR_UNSUPPORTED;
   const long long items = (long long)n_tokens * H;
-  const dim3 grid((unsigned)((items + hs::PA_WARPS - 1) / hs::PA_WARPS)), blk(hs::PA_WARPS * 32);
+  if (items > 0x7fffffffLL) return HS_ERR_TOO_LARGE;
+  const dim3 grid((unsigned)items), blk(hs::PA_WARPS * 32);
   cudaStream_t st = (cudaStream_t)stream;
   const bool pdl = hs_pdl_enabled();
   // 16-byte reads of a key row need rows that start and end on 16 bytes

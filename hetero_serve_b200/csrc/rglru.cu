@@ -20,8 +20,9 @@
 namespace hs {
 
 constexpr int RG_CH = 32;        // channels a block covers (one a lane)
-constexpr int RG_PARTS = 16;     // segments a portion is cut into (one a warp)
+constexpr int RG_PARTS = 32;     // segments a portion is cut into (one a warp)
 constexpr int RG_MIN_SEG = 8;    // shortest segment: short portions use fewer warps
+constexpr int RG_AHEAD = 4;      // steps whose inputs are in flight together
 
 __global__ void __launch_bounds__(256)
 rglru_conv_kernel(float* __restrict__ u, const float* __restrict__ proj, int proj_stride,
@@ -92,12 +93,24 @@ rglru_scan_kernel(TO* __restrict__ out, float* __restrict__ state, int state_str
   const float S0 = live ? st[c] : 0.f;          // read before the barrier: the last segment's
   float A = 1.f, D = 0.f;                        // owner stores the new state behind it
   if (live && !single) {
-    for (int i = lo; i < hi; ++i) {
-      const size_t t = (size_t)(t0 + i);
-      const RgStep s = rg_step(z[t * 2 * C + zc] + br, z[t * 2 * C + zc + n_per] + bi,
-                               u[t * C + c], rt, scale);
-      A *= s.a;
-      D = fmaf(s.a, D, s.d);
+    // RG_AHEAD steps' inputs are loaded before the first is used (rows past the segment's end
+    // read its first row again and are dropped)
+    for (int i = lo; i < hi; i += RG_AHEAD) {
+      float zr[RG_AHEAD], zi[RG_AHEAD], uu[RG_AHEAD];
+#pragma unroll
+      for (int k = 0; k < RG_AHEAD; ++k) {
+        const size_t t = (size_t)(t0 + (i + k < hi ? i + k : lo));
+        zr[k] = z[t * 2 * C + zc];
+        zi[k] = z[t * 2 * C + zc + n_per];
+        uu[k] = u[t * C + c];
+      }
+#pragma unroll
+      for (int k = 0; k < RG_AHEAD; ++k) {
+        if (i + k >= hi) break;
+        const RgStep s = rg_step(zr[k] + br, zi[k] + bi, uu[k], rt, scale);
+        A *= s.a;
+        D = fmaf(s.a, D, s.d);
+      }
     }
   }
   s_a[part][lane] = A;
@@ -107,12 +120,23 @@ rglru_scan_kernel(TO* __restrict__ out, float* __restrict__ state, int state_str
   // pass 2: the carries of the segments before, in index order, then the segment itself
   float S = S0;
   for (int p = 0; p < part; ++p) S = fmaf(s_a[p][lane], S, s_d[p][lane]);
-  for (int i = lo; i < hi; ++i) {
-    const size_t t = (size_t)(t0 + i);
-    const RgStep s = rg_step(z[t * 2 * C + zc] + br, z[t * 2 * C + zc + n_per] + bi,
-                             u[t * C + c], rt, scale);
-    S = fmaf(s.a, S, s.d);
-    out[t * C + c] = from_f<TO>(S * gelu_tanh(proj[t * proj_stride + y_off + c]));
+  for (int i = lo; i < hi; i += RG_AHEAD) {
+    float zr[RG_AHEAD], zi[RG_AHEAD], uu[RG_AHEAD], yy[RG_AHEAD];
+#pragma unroll
+    for (int k = 0; k < RG_AHEAD; ++k) {
+      const size_t t = (size_t)(t0 + (i + k < hi ? i + k : lo));
+      zr[k] = z[t * 2 * C + zc];
+      zi[k] = z[t * 2 * C + zc + n_per];
+      uu[k] = u[t * C + c];
+      yy[k] = proj[t * proj_stride + y_off + c];
+    }
+#pragma unroll
+    for (int k = 0; k < RG_AHEAD; ++k) {
+      if (i + k >= hi) break;
+      const RgStep s = rg_step(zr[k] + br, zi[k] + bi, uu[k], rt, scale);
+      S = fmaf(s.a, S, s.d);
+      out[(size_t)(t0 + i + k) * C + c] = from_f<TO>(S * gelu_tanh(yy[k]));
+    }
   }
   if (hi == n) {
     st[c] = S;
@@ -128,12 +152,15 @@ rglru_scan_kernel(TO* __restrict__ out, float* __restrict__ state, int state_str
 }
 
 // One token of every request: convolution, gates, decay, the state's step and the history in
-// ONE launch.  A block takes one (token, part of the channels): the part's n convolved inputs go
-// to shared memory, the 2n gate sums are formed from them as the block-diagonal kernel forms
-// them (four warps each sum a quarter of the inputs for 32 columns at a time, the quarters are
-// added in the same order), then a thread per channel steps the state.  Every sum has the order
-// it has on the path of three launches, so a token's result is the same bits on both.
-constexpr int RS_THREADS = 128;
+// ONE launch.  A block takes one part of the channels for up to RS_TT tokens (so the part's gate
+// matrices are read once for all of them): the part's n convolved inputs of each token go to
+// shared memory, the 2n gate sums are formed from them as the block-diagonal kernel forms them
+// (a warp sums a quarter of the inputs for 32 columns, the four quarters are added in the same
+// order; eight such column groups are in flight), then a thread per (token, channel) steps the
+// state.  Every sum has the order it has on the path of three launches, so a token's result is
+// the same bits on both.
+constexpr int RS_THREADS = 1024;
+constexpr int RS_TT = 8;
 
 template <typename TO>
 __global__ void __launch_bounds__(RS_THREADS)
@@ -142,51 +169,74 @@ rglru_step_kernel(TO* __restrict__ out, float* __restrict__ state, int state_str
                   const float* __restrict__ cw, const float* __restrict__ cb,
                   const float* __restrict__ w_gates, const float* __restrict__ b_gates,
                   const float* __restrict__ rate, const int* __restrict__ tok_req,
-                  const int* __restrict__ req_slot, int C, int n_per, int taps, float scale) {
-  extern __shared__ float s_rs[];                  // u [n_per] | partial sums [4][2 n_per]
+                  const int* __restrict__ req_slot, int n_tokens, int C, int n_per, int taps,
+                  float scale) {
+  extern __shared__ float s_rs[];            // u [RS_TT][n_per] | partial sums [4][RS_TT][2 n_per]
+  __shared__ int s_slot[RS_TT];
   float* s_u = s_rs;
-  float* s_z = s_rs + n_per;
+  float* s_z = s_rs + RS_TT * n_per;
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.y, blk = blockIdx.x;
-  const int r = tok_req[t];
-  if (r < 0) return;
-  float* st = state + (size_t)req_slot[r] * state_stride;
-  float* hist = st + C;                            // [taps-1][C], oldest first
-  const float* row = proj + (size_t)t * proj_stride;
+  const int blk = blockIdx.x, t0 = blockIdx.y * RS_TT;
+  if (threadIdx.x < RS_TT) {
+    const int t = t0 + threadIdx.x;
+    const int r = t < n_tokens ? tok_req[t] : -1;
+    s_slot[threadIdx.x] = r >= 0 ? req_slot[r] : -1;
+  }
+  __syncthreads();
   const int c0 = blk * n_per;
-  for (int i = threadIdx.x; i < n_per; i += RS_THREADS) {
+  for (int idx = threadIdx.x; idx < RS_TT * n_per; idx += RS_THREADS) {
+    const int tt = idx / n_per, i = idx - tt * n_per;
     const int c = c0 + i;
-    float acc = cb[c];
-    for (int j = 0; j < taps; ++j) {
-      const float v = j == 0 ? row[x_off + c] : hist[(size_t)(taps - 1 - j) * C + c];
-      acc = fmaf(cw[(size_t)c * taps + (taps - 1 - j)], v, acc);
+    float acc = 0.f;
+    if (s_slot[tt] >= 0) {
+      const float* hist = state + (size_t)s_slot[tt] * state_stride + C;   // [taps-1][C]
+      const float* row = proj + (size_t)(t0 + tt) * proj_stride;
+      acc = cb[c];
+      for (int j = 0; j < taps; ++j) {
+        const float v = j == 0 ? row[x_off + c] : hist[(size_t)(taps - 1 - j) * C + c];
+        acc = fmaf(cw[(size_t)c * taps + (taps - 1 - j)], v, acc);
+      }
     }
-    s_u[i] = acc;
+    s_u[idx] = acc;
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quarter = warp & 3, lane_group = warp >> 2;          // 8 column groups in flight
   const int n_out = 2 * n_per;
   const int per = (n_per + 3) / 4;
-  const int k_lo = warp * per, k_hi = min(n_per, k_lo + per);
+  const int k_lo = quarter * per, k_hi = min(n_per, k_lo + per);
   const float* wg = w_gates + (size_t)blk * n_per * n_out;
-  for (int j0 = 0; j0 < n_out; j0 += 32) {
+  for (int j0 = lane_group * 32; j0 < n_out; j0 += (RS_THREADS / 128) * 32) {
     const int j = j0 + lane;
-    float acc = 0.f;
-    if (j < n_out) {
+    if (j >= n_out) continue;
+    float acc[RS_TT];
+#pragma unroll
+    for (int tt = 0; tt < RS_TT; ++tt) acc[tt] = 0.f;
 #pragma unroll 8
-      for (int kk = k_lo; kk < k_hi; ++kk) acc = fmaf(s_u[kk], wg[(size_t)kk * n_out + j], acc);
-      s_z[warp * n_out + j] = acc;
+    for (int kk = k_lo; kk < k_hi; ++kk) {
+      const float wv = wg[(size_t)kk * n_out + j];
+#pragma unroll
+      for (int tt = 0; tt < RS_TT; ++tt) acc[tt] = fmaf(s_u[tt * n_per + kk], wv, acc[tt]);
     }
+#pragma unroll
+    for (int tt = 0; tt < RS_TT; ++tt) s_z[(quarter * RS_TT + tt) * n_out + j] = acc[tt];
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < n_per; i += RS_THREADS) {
-    const int c = c0 + i;
-    const float zr = ((s_z[i] + s_z[n_out + i]) + s_z[2 * n_out + i]) + s_z[3 * n_out + i];
-    const float zi = ((s_z[n_per + i] + s_z[n_out + n_per + i]) + s_z[2 * n_out + n_per + i]) +
-                     s_z[3 * n_out + n_per + i];
+  const int qs = RS_TT * n_out;                                  // one quarter's sums
+  for (int idx = threadIdx.x; idx < RS_TT * n_per; idx += RS_THREADS) {
+    const int tt = idx / n_per, i = idx - tt * n_per;
+    if (s_slot[tt] < 0) continue;
+    const int c = c0 + i, t = t0 + tt;
+    const float* zq = s_z + tt * n_out;
+    const float zr = ((zq[i] + zq[qs + i]) + zq[2 * qs + i]) + zq[3 * qs + i];
+    const float zi = ((zq[n_per + i] + zq[qs + n_per + i]) + zq[2 * qs + n_per + i]) +
+                     zq[3 * qs + n_per + i];
     const int zc = blk * n_out + i;
-    const RgStep s = rg_step(zr + b_gates[zc], zi + b_gates[zc + n_per], s_u[i], rate[c], scale);
+    const RgStep s = rg_step(zr + b_gates[zc], zi + b_gates[zc + n_per], s_u[idx], rate[c], scale);
+    float* st = state + (size_t)s_slot[tt] * state_stride;
+    float* hist = st + C;
+    const float* row = proj + (size_t)t * proj_stride;
     const float S = fmaf(s.a, st[c], s.d);
     out[(size_t)t * C + c] = from_f<TO>(S * gelu_tanh(row[y_off + c]));
     st[c] = S;
@@ -242,7 +292,7 @@ HS_EXPORT int hs_rglru_scan(void* out, float* state, int state_stride, const flo
 }
 
 // One token a request (tokens whose request row is negative are skipped).  The gate matrices
-// are float32 [blocks, n (summed), 2n (r | i)].  Refuses parts too large for shared memory.
+// are float32 [blocks, n (summed), 2n (r | i)].  Refuses parts of more than 256 channels.
 HS_EXPORT int hs_rglru_step(void* out, float* state, int state_stride, const float* proj,
                             int proj_stride, int y_off, int x_off, const float* cw,
                             const float* cb, const float* w_gates, const float* b_gates,
@@ -255,21 +305,35 @@ HS_EXPORT int hs_rglru_step(void* out, float* state, int state_stride, const flo
   if (C <= 0 || blocks <= 0 || C % blocks || taps < 1 || state_stride < C * taps)
     return HS_ERR_UNSUPPORTED;
   const int n_per = C / blocks;
-  const size_t smem = (size_t)9 * n_per * sizeof(float);
-  if (smem > 40 * 1024) return HS_ERR_UNSUPPORTED;
+  // parts of up to 256 channels: beyond that a block's walk over its gate matrices takes
+  // longer than the three launches, whose grids spread it over the device
+  if (n_per > 256) return HS_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)9 * hs::RS_TT * n_per * sizeof(float);
   if (n_tokens <= 0) return HS_OK;
-  if (n_tokens > 65535) return HS_ERR_TOO_LARGE;
-  const dim3 grid(blocks, n_tokens), block(hs::RS_THREADS);
+  const int tiles = (n_tokens + hs::RS_TT - 1) / hs::RS_TT;
+  if (tiles > 65535) return HS_ERR_TOO_LARGE;
+  const dim3 grid(blocks, tiles), block(hs::RS_THREADS);
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
+  static bool sized = false;
+  if (!sized) {
+    const int most = 9 * hs::RS_TT * 256 * (int)sizeof(float);
+    e = cudaFuncSetAttribute(hs::rglru_step_kernel<__nv_bfloat16>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(hs::rglru_step_kernel<float>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e != cudaSuccess) return (int)e;
+    sized = true;
+  }
   if (out_dtype == HS_DT_BF16)
     e = hs_launch(hs::rglru_step_kernel<__nv_bfloat16>, grid, block, smem, st, hs_pdl_enabled(),
                   (__nv_bfloat16*)out, state, state_stride, proj, proj_stride, y_off, x_off, cw,
-                  cb, w_gates, b_gates, rate, tok_req, req_slot, C, n_per, taps, scale);
+                  cb, w_gates, b_gates, rate, tok_req, req_slot, n_tokens, C, n_per, taps, scale);
   else if (out_dtype == HS_DT_F32)
     e = hs_launch(hs::rglru_step_kernel<float>, grid, block, smem, st, hs_pdl_enabled(),
                   (float*)out, state, state_stride, proj, proj_stride, y_off, x_off, cw, cb,
-                  w_gates, b_gates, rate, tok_req, req_slot, C, n_per, taps, scale);
+                  w_gates, b_gates, rate, tok_req, req_slot, n_tokens, C, n_per, taps, scale);
   else
     return HS_ERR_UNSUPPORTED;
   return e == cudaSuccess ? HS_OK : (int)e;

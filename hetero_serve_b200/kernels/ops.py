@@ -1631,8 +1631,8 @@ class CudaOps:
                    req_slot, *, channels, blocks, taps, decay_scale, y_off, x_off) -> bool:
         """``rglru_conv``, the gates' block-diagonal product and ``rglru_scan`` for a step in
         which every request brings ONE token, in one launch and with the same bits.
-        ``w_gates`` float32 [blocks, n, 2n].  False (nothing done) for parts of the channels
-        too large for its shared memory."""
+        ``w_gates`` float32 [blocks, n, 2n].  False (nothing done) for parts of more than 256
+        channels, which the three launches spread better over the device."""
         for name, v in (("proj", proj), ("state", state)):
             _want(v, name, torch.float32, 2)
         _want(out, "out", _FLOATS, 2)
