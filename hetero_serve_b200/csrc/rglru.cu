@@ -11,16 +11,18 @@
 //
 // Everything here is float32 (only `out`, the input of the output projection, is written in
 // the compute type).  The recurrence of one (request, channel) is linear, S <- a S + d, so the
-// portion is cut into up to RG_PARTS segments of equal length: every segment is first reduced
+// portion is cut into up to 32 or 64 segments of equal length: every segment is first reduced
 // to its pair (product of a, result from zero), the carries are chained in index order, and
-// the segment is walked again from its carry.  The cut depends on the portion's length only;
+// the segment is walked again from its carry.  The cut depends on the portion's length and the layer's channels only;
 // sqrt(1 - a^2) is formed as sqrt(-expm1(2 log a)), which keeps its digits when a is near 1.
 #include "common.cuh"
 
 namespace hs {
 
-constexpr int RG_CH = 32;        // channels a block covers (one a lane)
-constexpr int RG_PARTS = 32;     // segments a portion is cut into (one a warp)
+constexpr int RG_THREADS = 1024; // a block: RG_CH channels x RG_THREADS / RG_CH segments
+constexpr int RG_WIDE = 1024;    // up to this many channels a block covers 16 of them and cuts a
+                                 // portion into 64 segments (more blocks than 32 channels give,
+                                 // which few channels need to fill the device); beyond, 32 and 32
 constexpr int RG_MIN_SEG = 8;    // shortest segment: short portions use fewer warps
 constexpr int RG_AHEAD = 4;      // steps whose inputs are in flight together
 
@@ -60,14 +62,15 @@ __device__ __forceinline__ RgStep rg_step(float zr, float zi, float uu, float ra
   return s;
 }
 
-template <typename TO>
-__global__ void __launch_bounds__(RG_CH * RG_PARTS)
+template <typename TO, int RG_CH>
+__global__ void __launch_bounds__(RG_THREADS)
 rglru_scan_kernel(TO* __restrict__ out, float* __restrict__ state, int state_stride,
                   const float* __restrict__ u, const float* __restrict__ z,
                   const float* __restrict__ proj, int proj_stride, int y_off, int x_off,
                   const float* __restrict__ b_gates, const float* __restrict__ rate,
                   const int* __restrict__ req_start, const int* __restrict__ req_len,
                   const int* __restrict__ req_slot, int C, int n_per, int taps, float scale) {
+  constexpr int RG_PARTS = RG_THREADS / RG_CH;
   __shared__ float s_a[RG_PARTS][RG_CH], s_d[RG_PARTS][RG_CH];
   pdl_trigger();
   pdl_wait();
@@ -75,7 +78,7 @@ rglru_scan_kernel(TO* __restrict__ out, float* __restrict__ state, int state_str
   const int n = req_len[r];
   if (n <= 0) return;
   const int t0 = req_start[r];
-  const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
+  const int lane = threadIdx.x % RG_CH, part = threadIdx.x / RG_CH;
   const int c = blockIdx.x * RG_CH + lane;
   const bool live = c < C;
   int seg = (n + RG_PARTS - 1) / RG_PARTS;
@@ -275,19 +278,23 @@ HS_EXPORT int hs_rglru_scan(void* out, float* state, int state_stride, const flo
     return HS_ERR_UNSUPPORTED;
   if (n_requests <= 0) return HS_OK;
   if (n_requests > 65535) return HS_ERR_TOO_LARGE;
-  const dim3 grid((C + hs::RG_CH - 1) / hs::RG_CH, n_requests), block(hs::RG_CH * hs::RG_PARTS);
+  // the cut depends on the model's channels only, never on the batch
+  const int ch = C <= hs::RG_WIDE ? 16 : 32;
+  const dim3 grid((C + ch - 1) / ch, n_requests), block(hs::RG_THREADS);
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-  if (out_dtype == HS_DT_BF16)
-    e = hs_launch(hs::rglru_scan_kernel<__nv_bfloat16>, grid, block, 0, st, hs_pdl_enabled(),
-                  (__nv_bfloat16*)out, state, state_stride, u, z, proj, proj_stride, y_off, x_off,
-                  b_gates, rate, req_start, req_len, req_slot, C, C / blocks, taps, scale);
-  else if (out_dtype == HS_DT_F32)
-    e = hs_launch(hs::rglru_scan_kernel<float>, grid, block, 0, st, hs_pdl_enabled(),
-                  (float*)out, state, state_stride, u, z, proj, proj_stride, y_off, x_off,
-                  b_gates, rate, req_start, req_len, req_slot, C, C / blocks, taps, scale);
-  else
+#define HS_RG_SCAN(TO, CH)                                                                       \
+  e = hs_launch(hs::rglru_scan_kernel<TO, CH>, grid, block, 0, st, hs_pdl_enabled(), (TO*)out,   \
+                state, state_stride, u, z, proj, proj_stride, y_off, x_off, b_gates, rate,       \
+                req_start, req_len, req_slot, C, C / blocks, taps, scale)
+  if (out_dtype == HS_DT_BF16) {
+    if (ch == 16) HS_RG_SCAN(__nv_bfloat16, 16); else HS_RG_SCAN(__nv_bfloat16, 32);
+  } else if (out_dtype == HS_DT_F32) {
+    if (ch == 16) HS_RG_SCAN(float, 16); else HS_RG_SCAN(float, 32);
+  } else {
     return HS_ERR_UNSUPPORTED;
+  }
+#undef HS_RG_SCAN
   return e == cudaSuccess ? HS_OK : (int)e;
 }
 

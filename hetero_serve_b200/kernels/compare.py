@@ -165,6 +165,12 @@ def _flops_and_bytes(name, args, kw, batch):
         if name == "rglru_scan":
             out, _state, u, z = args[:4]
             return 0, _nbytes(out, u, z) + u.numel() * 4
+        if name == "rglru_step":
+            out, state, proj = args[:3]
+            w_gates = args[5]
+            T, C = out.shape
+            return (4 * T * C * w_gates.shape[1],
+                    _nbytes(out, proj, w_gates) + 2 * T * C * kw["taps"] * 4)
         if name == "pooled_prepare":
             q_out, pool, proj = args[:3]
             rows = q_out.shape[0] * kw["n_kv_heads"] * (kw["head_dim"] + kw["value_dim"])
