@@ -118,7 +118,8 @@ def _recurrence_weights(C, B, taps, seed):
 
 
 @pytest.mark.parametrize("dtype, tol", [(F32, 5e-6), (BF16, 1e-2)])
-@pytest.mark.parametrize("C, B, taps", [(40, 2, 4), (36, 3, 3), (24, 1, 1), (256, 4, 4), (70, 7, 2)])
+@pytest.mark.parametrize("C, B, taps", [(40, 2, 4), (36, 3, 3), (24, 1, 1), (256, 4, 4), (70, 7, 2),
+                                        (1056, 8, 2)])
 def test_recurrence_in_portions_and_batches(ops, dtype, tol, C, B, taps):
     """Three requests side by side in slots that are in no order, cut into portions of unequal
     length (one shorter than the convolution's history, one long enough to be scanned in
@@ -349,6 +350,46 @@ def test_pooled_window_attention(ops, dtype, tol, H, G, D, V, window, pool, rot,
             fed[r] += k
             at += k
     assert int(status.item()) == 0 and fed == {"a": 150, "b": 77}
+
+
+@pytest.mark.parametrize("dtype, tol", [(F32, 1e-5), (BF16, 3e-2)])
+@pytest.mark.parametrize("H, G, D, V, window, pool", [(2, 1, 16, 24, 300, 4), (4, 2, 64, 64, 270, 2)])
+def test_a_token_with_hundreds_of_keys(ops, dtype, tol, H, G, D, V, window, pool):
+    """Positions up to 700 under a window of some hundred keys: a token sees more rows (token
+    rows and mean rows) than one round of all the warps of its block takes, so every warp has
+    keys, some walk twice, and their shares are joined.  Every position is compared."""
+    W, w, m = _attention_case(H, G, D, V, window, pool, 8, 300.0, 1.3 / math.sqrt(D), 70)
+    w64 = {k: v.double() for k, v in w.items()}
+    eps, page, n = 1e-5, 16, 700
+    rows = rnd(n, W, seed=71)
+    if dtype == BF16:
+        rows = rows.to(BF16).float()
+    want = P.pooled_window_attention(rows.double(), w64, "m.", m, eps)
+    n_pages = 72
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(72)).tolist()
+    table = dev(torch.tensor([perm[:44]], dtype=I32))
+    ctable = dev(torch.tensor([perm[44:68]], dtype=I32))
+    fine = torch.full((n_pages, G, page, D + V), float("nan"), dtype=dtype, device=DEV)
+    coarse = torch.full((n_pages, G, page, D + V), float("nan"), dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=I32, device=DEV)
+    fq, fv = dev(_frequencies(300.0, 8)), dev(_frequencies(300.0, V))
+    wq, wk = dev(w["m.q.norm"], w["m.k.norm"])
+    sizes = dict(n_heads=H, n_kv_heads=G, head_dim=D, value_dim=V, page_size=page, status=status)
+    fed = 0
+    for k in (333, 1, 1, 360, 1, 1, 1, 1, 1):
+        proj = dev(rows[fed:fed + k])
+        tok_pos, tok_req = ints(range(fed, fed + k)), ints([0] * k)
+        q = torch.zeros(k, H * D, device=DEV)
+        ops.pooled_prepare(q, fine, proj, wq, wk, fq, fv, table, tok_pos, tok_req, rot_dims=8,
+                           eps=eps, writes=True, **sizes)
+        ops.pooled_means(coarse, ctable, fine, table, tok_pos, tok_req, n_kv_heads=G, row=D + V,
+                         block=pool, page_size=page, status=status)
+        out = torch.full((k, H * V), float("nan"), dtype=dtype, device=DEV)
+        ops.pooled_attention(out, q, fine, table, coarse, ctable, tok_pos, tok_req, fv,
+                             window=window, block=pool, scale=m["scale"], plan=None, **sizes)
+        close(out, want[fed:fed + k], tol)
+        fed += k
+    assert int(status.item()) == 0 and fed == n
 
 
 def test_attention_reports_a_page_that_is_missing(ops):
