@@ -67,12 +67,14 @@ class GroupSpec:
     ``chunk == c`` keeps the positions of the chunk of c the request's next token falls in
     (chunks counted from position 0).  ``stride == s > 1``: the group keeps one row for every
     complete block of s positions (all of them: no window), so a page holds ``page_size``
-    blocks."""
+    blocks.  ``keep_first == f`` beside a window: the pages of positions < f are never given
+    back while the request lives."""
 
     window: int = 0
     chunk: int = 0
     num_pages: int | None = None      # None → the manager's default
     stride: int = 1
+    keep_first: int = 0
 
 
 class PagePool:
@@ -391,7 +393,8 @@ class CacheManager:
                 first_needed = max(first_needed, new_len // g.chunk * g.chunk)
             keep_from = first_needed // self.page_size
             table = req.tables[gi]
-            for i in range(req.first_live[gi], min(keep_from, len(table))):
+            kept = -(-g.keep_first // self.page_size) if g.keep_first > 0 else 0
+            for i in range(max(req.first_live[gi], kept), min(keep_from, len(table))):
                 if table[i] >= 0:
                     self.pools[gi].drop(table[i])
                     table[i] = -1

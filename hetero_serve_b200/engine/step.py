@@ -258,6 +258,7 @@ class Runner:
         self.manager = CacheManager(
             [GroupSpec(window=g.window, chunk=getattr(g, "chunk", 0),
                        stride=getattr(g, "stride", 1),
+                       keep_first=getattr(g, "keep_first", 0),
                        num_pages=(-(-num_pages // g.stride) + max_requests
                                   if getattr(g, "stride", 1) > 1 else None))
              for g in model.cache_groups], num_pages, page_size,

@@ -54,7 +54,9 @@ class CacheRequest:
     ``pool`` the mixer also keeps, for the whole sequence, one row of the same shape for every
     block of that many positions (block b: positions b * pool .. b * pool + pool - 1, written
     once the block is complete); these rows live in a companion page group whose pages hold
-    ``page_size`` blocks each, and reach the mixer as ``cache.coarse``."""
+    ``page_size`` blocks each, and reach the mixer as ``cache.coarse``.  With ``window`` and
+    ``keep_first`` the rows of the first ``keep_first`` positions stay readable for the whole
+    sequence (every query sees them beside its window)."""
 
     kv_heads: int
     head_dim: int
@@ -62,6 +64,7 @@ class CacheRequest:
     planes: int = 2
     chunk: int = 0
     pool: int = 0
+    keep_first: int = 0
 
 
 class Part:

@@ -149,15 +149,20 @@ class SandwichNormBlock(Block):
     rows of the norm in front of the feed-forward.  A layer may leave ``norm2``,
     ``feed_forward`` and ``norm2b`` out (all or none): it then ends after the mixer.  When the
     block that runs next is of this arrangement too, the layer's last launch also forms the
-    rows of THAT block's first norm (``ctx.normed_ahead``), which then skips it."""
+    rows of THAT block's first norm (``ctx.normed_ahead``), which then skips it.
+
+    ``side`` (optional, a feed-forward part) runs last and reads the STREAM itself, not a
+    normed copy: ``x += side(x)``.  It is handed ``then=(norm, out)`` like the norms, so that a
+    part that can form the next block's first norm in its last launch does so; with any other
+    part nothing is formed ahead."""
 
     slots = {"norm1": "norm", "mixer": "mixer", "norm1b": "norm", "norm2": "norm",
-             "feed_forward": "feed_forward", "norm2b": "norm"}
-    optional = ("norm2", "feed_forward", "norm2b")
+             "feed_forward": "feed_forward", "norm2b": "norm", "side": "feed_forward"}
+    optional = ("norm2", "feed_forward", "norm2b", "side")
 
     def __init__(self, spec: LayerSpec):
         super().__init__(spec)
-        present = [getattr(self, n) is not None for n in self.optional]
+        present = [getattr(self, n) is not None for n in ("norm2", "feed_forward", "norm2b")]
         if any(present) != all(present):
             raise ValueError("arrangement 'sandwich_norm': norm2, feed_forward and norm2b "
                              "come together")
@@ -176,14 +181,23 @@ class SandwichNormBlock(Block):
             self.norm1.forward(ctx, h, x)
         nxt = getattr(ctx, "next_block", None)
         ahead = (nxt.norm1, h) if isinstance(nxt, SandwichNormBlock) else None
+        side_ahead = self.side is not None and getattr(self.side, "forms_next_norm", False)
+        if self.side is not None and not side_ahead:
+            ahead = None                      # the stream still changes behind the last norm
         ctx.normed_ahead = ahead is not None
+        last = None if self.side is not None else ahead
         out = OutputNormBlock._run(self.mixer, ctx, h, y, cache)
         if not self.has_ff:
-            self.norm1b.add_normed(ctx, x, out, then=ahead)
-            return
-        self.norm1b.add_normed(ctx, x, out, then=(self.norm2, h))
-        out = OutputNormBlock._run(self.feed_forward, ctx, h, y)
-        self.norm2b.add_normed(ctx, x, out, then=ahead)
+            self.norm1b.add_normed(ctx, x, out, then=last)
+        else:
+            self.norm1b.add_normed(ctx, x, out, then=(self.norm2, h))
+            out = OutputNormBlock._run(self.feed_forward, ctx, h, y)
+            self.norm2b.add_normed(ctx, x, out, then=last)
+        if self.side is not None:
+            if side_ahead:
+                self.side.forward(ctx, h, x, then=ahead)
+            else:
+                self.side.forward(ctx, h, x)
 
 
 _ARRANGEMENTS: dict[str, Callable[[LayerSpec], Block]] = {"pre_norm": PreNormBlock,
@@ -209,6 +223,7 @@ class CacheGroup:
     planes: int = 2                 # rows kept per token and head (keys and values: two)
     chunk: int = 0                  # > 0: only the rows of the chunk the request is in are kept
     stride: int = 1                 # > 1: one row per block of this many positions
+    keep_first: int = 0             # with a window: the first positions' rows stay as well
 
 
 class Model:
@@ -269,7 +284,8 @@ class Model:
         for entry in sorted(entry_req):
             groups.setdefault(entry_req[entry], []).append(entry)
         self.cache_groups: list[CacheGroup] = [
-            CacheGroup(r.kv_heads, r.head_dim, r.window, tuple(es), r.planes, r.chunk)
+            CacheGroup(r.kv_heads, r.head_dim, r.window, tuple(es), r.planes, r.chunk,
+                       keep_first=r.keep_first)
             for r, es in groups.items()]
         self.entry_location: dict[int, tuple[int, int]] = {}
         for gi, g in enumerate(self.cache_groups):

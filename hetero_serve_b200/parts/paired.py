@@ -99,3 +99,47 @@ class NormedMixerPair(Mixer):
 
 
 register_mixer("normed_pair", NormedMixerPair)
+
+
+class SummedMixerPair(Mixer):
+    """Two mixers side by side whose outputs are added: ``out = left(x) + right(x)``.  Weights
+    of the two halves are the sub-mixers' business (an ``out_scale`` of their own); at most one
+    of them may keep a cache entry and at most one a state.  The first writes the block, the
+    second adds into it."""
+
+    writes_fresh = True
+
+    def __init__(self, *, left: PartSpec, right: PartSpec):
+        self.subs = (build_part("mixer", left), build_part("mixer", right))
+        if sum(s.cache_request() is not None for s in self.subs) > 1 or \
+                sum(s.state_shape() is not None for s in self.subs) > 1:
+            raise ValueError("both mixers of a pair keep a cache entry (or both a state); a "
+                             "layer call addresses one of each")
+        self.capturable = all(s.capturable for s in self.subs)
+
+    def tensor_requests(self):
+        req = {}
+        for s in self.subs:
+            req.update(s.tensor_requests())
+        return req
+
+    def bind(self, tensors):
+        for s in self.subs:
+            s.bind({n: tensors[n] for n in s.tensor_requests()})
+
+    cache_request = NormedMixerPair.cache_request
+    state_shape = NormedMixerPair.state_shape
+
+    def forward(self, ctx, h, x, cache, fresh=False):
+        first = fresh
+        for s in self.subs:
+            if first and getattr(s, "writes_fresh", False):
+                s.forward(ctx, h, x, cache, fresh=True)
+            else:
+                if first:
+                    x.zero_()
+                s.forward(ctx, h, x, cache)
+            first = False
+
+
+register_mixer("summed_pair", SummedMixerPair)

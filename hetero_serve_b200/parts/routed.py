@@ -17,6 +17,10 @@ logits are chosen (the lower index wins a tie) and weighted by the softmax over 
 logits alone; and a second expert (``activation="silu"``): y = silu(W_gate h) * (W_up h).
 ``shared`` names a feed-forward (a :class:`PartSpec`) that runs for every token beside the
 experts and is added to their sum.
+
+A third rule (``scoring="table"``) has no router: an integer table [vocab, top] names the
+experts of every token id, each weighing 1/top; and a third expert (``activation="relu2"``) has
+no gate matrix: y = relu(W_up h)^2.
 """
 
 from __future__ import annotations
@@ -25,7 +29,7 @@ import torch
 
 from .base import FeedForward, TensorRequest, build_part, register_feed_forward
 
-SCORINGS = ("sigmoid_groups", "softmax_top")
+SCORINGS = ("sigmoid_groups", "softmax_top", "table")
 
 
 class RoutedExperts(FeedForward):
@@ -34,10 +38,10 @@ class RoutedExperts(FeedForward):
     def __init__(self, *, width: int, ff: int, experts: int, top: int, router: str,
                  expert_prefix: str, groups: int = 1, keep: int = 1, limit: float = 0.0,
                  scoring: str = "sigmoid_groups", activation: str = "clamped",
-                 router_bias: str | None = None, shared=None):
+                 router_bias: str | None = None, shared=None, table_rows: int = 0):
         if scoring not in SCORINGS:
             raise ValueError(f"unknown scoring {scoring!r}; known: {SCORINGS}")
-        if activation not in ("clamped", "silu"):
+        if activation not in ("clamped", "silu", "relu2"):
             raise ValueError(f"unknown expert activation {activation!r}")
         if scoring == "sigmoid_groups":
             if experts % groups:
@@ -48,9 +52,13 @@ class RoutedExperts(FeedForward):
                 raise ValueError("the grouped sigmoid rule takes no router bias")
         elif not 0 < top <= experts:
             raise ValueError(f"{top} chosen experts of {experts}")
+        if scoring == "table" and (table_rows <= 0 or router_bias is not None):
+            raise ValueError("the table rule needs the table's rows and takes no router bias")
+        self.table_rows = int(table_rows)
         self.width, self.ff, self.E, self.top = width, ff, experts, top
         self.groups, self.keep, self.limit = groups, keep, float(limit)
         self.scoring, self.activation = scoring, activation
+        self.gated = activation != "relu2"
         self.router_name, self.bias_name, self.prefix = router, router_bias, expert_prefix
         self.shared = build_part("feed_forward", shared) if shared is not None else None
         if self.shared is not None:
@@ -60,13 +68,17 @@ class RoutedExperts(FeedForward):
         return f"{self.prefix}{e}.{which}"
 
     def tensor_requests(self):
-        req = {self.router_name: TensorRequest((self.E, self.width), "float32")}
+        if self.scoring == "table":
+            req = {self.router_name: TensorRequest((self.table_rows, self.top), "int")}
+        else:
+            req = {self.router_name: TensorRequest((self.E, self.width), "float32")}
         if self.bias_name:
             req[self.bias_name] = TensorRequest((self.E,), "vector")
         if self.shared is not None:
             req.update(self.shared.tensor_requests())
         for e in range(self.E):
-            req[self._expert(e, "gate")] = TensorRequest((self.ff, self.width), "matrix")
+            if self.gated:
+                req[self._expert(e, "gate")] = TensorRequest((self.ff, self.width), "matrix")
             req[self._expert(e, "up")] = TensorRequest((self.ff, self.width), "matrix")
             req[self._expert(e, "down")] = TensorRequest((self.width, self.ff), "matrix")
         return req
@@ -79,15 +91,17 @@ class RoutedExperts(FeedForward):
         # prompt portions in bfloat16 form the logits as one product on the tensor cores (exact
         # products, float32 sums) when the router's values are bfloat16 numbers to begin with
         self.w_router_lp = None
-        first = tensors[self._expert(0, "gate")]
-        low = self.w_router.to(torch.bfloat16)
-        if first.dtype == torch.bfloat16 and torch.equal(low.to(torch.float32), self.w_router):
-            self.w_router_lp = low.contiguous()
+        first = tensors[self._expert(0, "up")]
+        if self.scoring != "table":
+            low = self.w_router.to(torch.bfloat16)
+            if first.dtype == torch.bfloat16 and torch.equal(low.to(torch.float32), self.w_router):
+                self.w_router_lp = low.contiguous()
 
         def stack(which):          # [E, out, in], as stored: the summed index runs fastest
             return torch.stack([tensors[self._expert(e, which)]
                                 for e in range(self.E)]).contiguous()
-        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        self.w_gate = stack("gate") if self.gated else None
+        self.w_up, self.w_down = stack("up"), stack("down")
 
     def forward(self, ctx, h, x, fresh=False):
         ops, T = ctx.ops, h.shape[0]
@@ -106,7 +120,10 @@ class RoutedExperts(FeedForward):
         if self.w_router_lp is not None and T >= 64:
             z = ctx.buffer("route_z", (T, self.E), torch.float32)
             ops.linear(z, h, self.w_router_lp)
-        if self.scoring == "softmax_top":
+        if self.scoring == "table":
+            ops.moe_route_table(idx, wts, self.w_router, ctx.tok_ids, ctx.tok_req, top=self.top,
+                                feedback=ctx.feedback)
+        elif self.scoring == "softmax_top":
             ops.moe_route_top(idx, wts, h, self.w_router, self.b_router, ctx.tok_req,
                               top=self.top, z=z)
         else:

@@ -125,7 +125,8 @@ def write_model_dir(out_dir: str | Path, config: Mapping | object, seed: int,
     if td is None:
         raise ConfigError(f"cannot store weights as {dtype!r}")
     if td != torch.float32:
-        tensors = {n: (t.to(td) if t.dim() >= 2 else t) for n, t in tensors.items()}
+        tensors = {n: (t.to(td) if t.dim() >= 2 and t.dtype.is_floating_point else t)
+                   for n, t in tensors.items()}
     cfg_out = dict(cfg_dict)
     cfg_out["torch_dtype"] = "bfloat16" if td == torch.bfloat16 else "float32"
     (out_dir / "config.json").write_text(json.dumps(cfg_out, indent=2) + "\n")

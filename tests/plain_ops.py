@@ -23,6 +23,9 @@ _ACT = {"none": lambda u: u, "gelu_tanh": gelu_new, "gelu_erf": gelu_erf,
         "relu2": lambda u: torch.relu(u) ** 2, "silu": lambda u: u * torch.sigmoid(u)}
 
 
+_GATE = {"silu": lambda u: u * torch.sigmoid(u), "sigmoid": torch.sigmoid}
+
+
 class PlainOps:
     name = "plain"
 
@@ -304,6 +307,18 @@ class PlainOps:
     def moe_experts(self, x, y, h, w_gate, w_up, w_down, sel_idx, sel_w, tok_req, *, limit,
                     act="clamped"):
         T, top = sel_idx.shape
+        if act == "relu2":
+            for t in range(T):
+                if int(tok_req[t]) < 0:
+                    continue
+                hv = h[t].to(self.cd)
+                add = torch.zeros(x.shape[1], dtype=self.cd)
+                for k in range(top):
+                    e = int(sel_idx[t, k])
+                    inner = torch.relu(w_up[e].to(self.cd) @ hv) ** 2
+                    add = add + sel_w[t, k].to(self.cd) * (w_down[e].to(self.cd) @ inner)
+                x[t] = (x[t].to(self.cd) + add).to(x.dtype)
+            return
         if act == "silu":
             for t in range(T):
                 if int(tok_req[t]) < 0:
@@ -435,7 +450,8 @@ class PlainOps:
                 out[t, hd * head_dim:(hd + 1) * head_dim] = o.to(out.dtype)
 
     def lightning_recurrence(self, o, state, proj, decay, req_start, req_len, req_slot, *, q_off,
-                             k_off, v_off, heads, dim, vdim, act="silu"):
+                             k_off, v_off, heads, dim, vdim, act="silu", tok_pos=None,
+                             freq=None, rot_dims=0, k_scale=1.0):
         f = _ACT[act]
         for r in range(req_start.shape[0]):
             n = int(req_len[r])
@@ -448,6 +464,10 @@ class PlainOps:
                 q = f(row[q_off:q_off + heads * dim]).view(heads, dim)
                 k = f(row[k_off:k_off + heads * dim]).view(heads, dim)
                 v = f(row[v_off:v_off + heads * vdim]).view(heads, vdim)
+                if freq is not None and rot_dims:
+                    q = self._turn_halves(q, int(tok_pos[t]), freq, rot_dims)
+                    k = self._turn_halves(k, int(tok_pos[t]), freq, rot_dims)
+                k = k * k_scale
                 for hd in range(heads):
                     S[hd] = decay[hd].to(self.cd) * S[hd] + torch.outer(k[hd], v[hd])
                     o[t, hd * vdim:(hd + 1) * vdim] = (S[hd].T @ q[hd]).to(o.dtype)
@@ -603,3 +623,122 @@ class PlainOps:
             if freq_v is not None:
                 o = self._turn_halves(o, i, freq_v, V, sign=-1.0)
             out[t] = o.reshape(-1).to(out.dtype)
+
+    # -- parts of the Mafuzen design ---------------------------------------------------------
+    @staticmethod
+    def _token(ids, t, feedback):
+        tok = int(ids[t])
+        return int(feedback[-(tok + 1)]) if tok < 0 and feedback is not None else tok
+
+    def gather_mul(self, out, g, table, tok_ids, tok_req, *, col_offset, feedback=None):
+        n, dim = out.shape
+        for t in range(n):
+            if int(tok_req[t]) < 0:
+                continue
+            e = table[self._token(tok_ids, t, feedback), col_offset:col_offset + dim]
+            out[t] = (g[t].to(self.cd) * e.to(self.cd)).to(out.dtype)
+
+    def moe_route_table(self, sel_idx, sel_w, table, tok_ids, tok_req, *, top, feedback=None):
+        for t in range(sel_idx.shape[0]):
+            if int(tok_req[t]) < 0:
+                continue
+            sel_idx[t] = table[self._token(tok_ids, t, feedback), :top].to(torch.int32)
+            sel_w[t] = 1.0 / top
+
+    def head_norm_gate(self, out, o, weight, gate, *, gate_offset, heads, dim, eps,
+                       gate_act="silu", out_scale=1.0):
+        n = out.shape[0]
+        v = self._rms(o[:n].to(self.cd).view(n, heads, dim), eps).reshape(n, heads * dim)
+        if weight is not None:
+            v = v * weight.to(self.cd)
+        if gate is not None:
+            v = v * _GATE[gate_act](gate[:n, gate_offset:gate_offset + heads * dim].to(self.cd))
+        out.copy_((v * out_scale).to(out.dtype))
+
+    def span_prepare(self, q_out, pool, proj, table, tok_pos, tok_req, *, n_heads, n_kv_heads,
+                     head_dim, value_dim, q_off, k_off, v_off, qk_norm, eps, writes, page_size,
+                     status):
+        H, G, D, V = n_heads, n_kv_heads, head_dim, value_dim
+        pv = pool.view(-1, G, page_size, D + V)
+        for t in range(q_out.shape[0]):
+            r = int(tok_req[t])
+            if r < 0:
+                continue
+            row = proj[t].to(self.cd)
+            q = row[q_off:q_off + H * D].view(H, D)
+            q_out[t] = (self._rms(q, eps) if qk_norm else q).reshape(-1).to(q_out.dtype)
+            if not writes:
+                continue
+            k = row[k_off:k_off + G * D].view(G, D)
+            v = k if v_off is None else row[v_off:v_off + G * V].view(G, V)
+            kn = self._rms(k, eps) if qk_norm else k
+            p = int(tok_pos[t])
+            page = int(table[r, p // page_size])
+            pv[page, :, p % page_size, :D] = kn.to(pool.dtype)
+            pv[page, :, p % page_size, D:] = v.to(pool.dtype)
+
+    def span_attention(self, out, q, pool, table, tok_pos, tok_req, *, n_heads, n_kv_heads,
+                       head_dim, value_dim, scale, slopes, window, keep_first, gate, gate_offset,
+                       out_scale, page_size, status, plan=None):
+        H, G, D, V = n_heads, n_kv_heads, head_dim, value_dim
+        pv = pool.view(-1, G, page_size, D + V)
+        for t in range(out.shape[0]):
+            r = int(tok_req[t])
+            if r < 0:
+                continue
+            i = int(tok_pos[t])
+            first = max(0, i - window + 1) if window > 0 else 0
+            js = list(range(min(keep_first, first))) + list(range(first, i + 1))
+            rows = torch.stack([pv[int(table[r, j // page_size]), :, j % page_size]
+                                for j in js]).to(self.cd)                     # [keys, G, D + V]
+            dist = torch.tensor([i - j for j in js], dtype=self.cd)
+            qt = q[t].to(self.cd).view(H, D)
+            for hd in range(H):
+                g = hd // (H // G)
+                s = (rows[:, g, :D] @ qt[hd]) * scale
+                if slopes is not None:
+                    s = s - slopes[hd].to(self.cd) * dist
+                o = torch.softmax(s, 0) @ rows[:, g, D:]
+                if gate is not None:
+                    o = o * torch.sigmoid(
+                        gate[t, gate_offset + hd * V:gate_offset + (hd + 1) * V].to(self.cd))
+                out[t, hd * V:(hd + 1) * V] = (o * out_scale).to(out.dtype)
+
+    def token_shift_mix(self, out, h, mu, state, tok_req, req_start, req_len, req_slot, *,
+                        state_offset):
+        W = h.shape[1]
+        for r in range(req_start.shape[0]):
+            n = int(req_len[r])
+            if n <= 0:
+                continue
+            t0, slot = int(req_start[r]), int(req_slot[r])
+            prev = state[slot, state_offset:state_offset + W].to(self.cd)
+            for t in range(t0, t0 + n):
+                cur = h[t].to(self.cd)
+                for s in range(out.shape[0]):
+                    out[s, t] = (cur + (prev - cur) * mu[s].to(self.cd)).to(out.dtype)
+                prev = cur
+            state[slot, state_offset:state_offset + W] = prev.to(state.dtype)
+
+    def timemix_decay(self, out, low, w2, w0):
+        n = out.shape[0]
+        lw = torch.tanh(low[:n].to(self.cd)) @ w2.to(self.cd).T + w0.to(self.cd)
+        out.copy_(torch.exp(-torch.exp(lw)).to(out.dtype))
+
+    def timemix_recurrence(self, o, state, r, k, v, w, u, req_start, req_len, req_slot, *,
+                           heads, dim):
+        H, D = heads, dim
+        uu = u.to(self.cd).view(H, D)
+        for q in range(req_start.shape[0]):
+            n = int(req_len[q])
+            if n <= 0:
+                continue
+            t0, slot = int(req_start[q]), int(req_slot[q])
+            S = state[slot, :H * D * D].to(self.cd).view(H, D, D).clone()
+            for t in range(t0, t0 + n):
+                rt, kt, vt, wt = (a[t].to(self.cd).view(H, D) for a in (r, k, v, w))
+                for hd in range(H):
+                    kv = torch.outer(kt[hd], vt[hd])
+                    o[t, hd * D:(hd + 1) * D] = ((S[hd] + uu[hd][:, None] * kv).T @ rt[hd]).to(o.dtype)
+                    S[hd] = wt[hd][:, None] * S[hd] + kv
+            state[slot, :H * D * D] = S.reshape(-1).to(state.dtype)
