@@ -13,7 +13,13 @@
 // and the recurrence fetches the next portion by cp.async while it walks the current one.  A
 // token's arithmetic is the same chain whatever the batch or the cut of the prompt: results are
 // bit-equal across both.
+//
+// Retention is the same recurrence with q and k turned by the token's position on their first
+// rot_dims numbers (number i pairs with i + rot_dims/2) and k scaled: with a table of
+// frequencies the rows are turned where they are activated (in the pass of its own, or while
+// they are staged), by the same expression in both places.
 #include "common.cuh"
+#include "rotary.cuh"
 
 namespace hs {
 
@@ -26,6 +32,23 @@ constexpr int LA_TOK = 16;           // tokens staged at a time (8 when dim is a
 __device__ __forceinline__ float la_act(float z, int act) {
   return act == HS_ACT_SILU ? z / (1.0f + expf(-z)) : z;
 }
+// entry d of a head's q or k vector `vec`: activated, turned by position `pos` when d lies in the
+// first rot_dims numbers (rot_dims 0: never), times `mul`
+__device__ __forceinline__ float la_entry(const float* __restrict__ vec, int d, int act,
+                                          int rot_dims, const float* __restrict__ freq, int pos,
+                                          float mul) {
+  float own = la_act(vec[d], act);
+  if (d < rot_dims) {
+    const int half = rot_dims >> 1;
+    const bool low = d < half;
+    const float partner = la_act(vec[low ? d + half : d - half], act);
+    float c, sn;
+    pair_angle(pos, freq[low ? d : d - half], &c, &sn);
+    const float cross = __fmul_rn(partner, sn);
+    own = fmaf(own, c, low ? -cross : cross);
+  }
+  return __fmul_rn(own, mul);
+}
 __device__ __forceinline__ void la_cp16(void* smem_dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src)
                : "memory");
@@ -34,16 +57,26 @@ __device__ __forceinline__ void la_cp16(void* smem_dst, const void* src) {
 // dst[t, :] = act(q | k | v columns of proj[t]) as one compact row of 2 H D + H V floats
 __global__ void lightning_act_kernel(float* __restrict__ dst, const float* __restrict__ proj,
                                      int n_tokens, int stride, int q_off, int k_off, int v_off,
-                                     int hd, int hv, int act) {
+                                     int hd, int hv, int act, int D,
+                                     const int* __restrict__ tok_pos,
+                                     const float* __restrict__ freq, int rot_dims,
+                                     float k_scale) {
   pdl_trigger();
   pdl_wait();
   const int row_len = 2 * hd + hv;
   for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
     const float* row = proj + (size_t)t * stride;
     float* out = dst + (size_t)t * row_len;
+    const int pos = rot_dims > 0 ? tok_pos[t] : 0;
     for (int c = threadIdx.x; c < row_len; c += blockDim.x) {
-      const int src = c < hd ? q_off + c : (c < 2 * hd ? k_off + c - hd : v_off + c - 2 * hd);
-      out[c] = la_act(row[src], act);
+      if (c < 2 * hd) {
+        const bool is_q = c < hd;
+        const int e = is_q ? c : c - hd, d = e % D;
+        out[c] = la_entry(row + (is_q ? q_off : k_off) + (e - d), d, act, rot_dims, freq, pos,
+                          is_q ? 1.0f : k_scale);
+      } else {
+        out[c] = la_act(row[v_off + c - 2 * hd], act);
+      }
     }
   }
 }
@@ -75,7 +108,9 @@ __device__ __forceinline__ float la_token(float (&s)[LA_ROWS], const float* kp, 
 __device__ __forceinline__ void la_stage(float* s_q, const float* __restrict__ proj, int tok,
                                          int here, int stride, int q_off, int k_off, int v_off,
                                          int h, int D, int V, int Dp, int cols, int v0, int ntok,
-                                         int act, int bulk) {
+                                         int act, int bulk, const int* __restrict__ tok_pos,
+                                         const float* __restrict__ freq, int rot_dims,
+                                         float k_scale) {
   float* s_k = s_q + ntok * Dp;
   float* s_v = s_k + ntok * Dp;
   if (bulk) {
@@ -99,8 +134,9 @@ __device__ __forceinline__ void la_stage(float* s_q, const float* __restrict__ p
       const int tt = e / D, d = e - tt * D;
       const float* row = proj + (size_t)(tok + tt) * stride + (size_t)h * D;
       const int at = tt * Dp + d / LA_ROWS * LA_PART + d % LA_ROWS;
-      s_q[at] = la_act(row[q_off + d], act);
-      s_k[at] = la_act(row[k_off + d], act);
+      const int pos = rot_dims > 0 ? tok_pos[tok + tt] : 0;
+      s_q[at] = la_entry(row + q_off, d, act, rot_dims, freq, pos, 1.0f);
+      s_k[at] = la_entry(row + k_off, d, act, rot_dims, freq, pos, k_scale);
     }
     for (int e = threadIdx.x; e < here * cols; e += LA_THREADS) {
       const int tt = e / cols, c = e - tt * cols;
@@ -116,7 +152,8 @@ lightning_kernel(float* __restrict__ o, float* __restrict__ state, const float* 
                  const float* __restrict__ decay, const int* __restrict__ req_start,
                  const int* __restrict__ req_len, const int* __restrict__ req_slot, int stride,
                  int q_off, int k_off, int v_off, int H, int D, int V, int P, int act, int ntok,
-                 int bulk) {
+                 int bulk, const int* __restrict__ tok_pos, const float* __restrict__ freq,
+                 int rot_dims, float k_scale) {
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
@@ -145,13 +182,14 @@ lightning_kernel(float* __restrict__ o, float* __restrict__ state, const float* 
     __syncthreads();
   }
   la_stage(smem, proj, t0, min(ntok, n), stride, q_off, k_off, v_off, h, D, V, Dp, cols, v0, ntok,
-           act, bulk);
+           act, bulk, tok_pos, freq, rot_dims, k_scale);
   int buf = 0;
   for (int base = 0; base < n; base += ntok, buf ^= 1) {
     const int here = min(ntok, n - base);
     if (base + ntok < n) {
       la_stage(smem + (buf ^ 1) * per_buf, proj, t0 + base + ntok, min(ntok, n - base - ntok), stride,
-               q_off, k_off, v_off, h, D, V, Dp, cols, v0, ntok, act, bulk);
+               q_off, k_off, v_off, h, D, V, Dp, cols, v0, ntok, act, bulk, tok_pos, freq, rot_dims,
+               k_scale);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -203,8 +241,11 @@ HS_EXPORT int hs_lightning_recurrence(float* o, float* state, const float* proj,
                                       const int* req_len, const int* req_slot, int n_requests,
                                       int n_tokens, int stride, int q_off, int k_off, int v_off,
                                       int H, int D, int V, int act, float* scratch,
-                                      void* stream) {
+                                      const int* tok_pos, const float* freq, int rot_dims,
+                                      float k_scale, void* stream) {
   if (!o || !state || !proj || !decay || !req_start || !req_len || !req_slot)
+    return HS_ERR_ARGUMENT;
+  if (rot_dims < 0 || rot_dims % 2 || rot_dims > D || (rot_dims > 0 && (!freq || !tok_pos)))
     return HS_ERR_ARGUMENT;
   if (H <= 0 || D <= 0 || V <= 0 || D > 16 * hs::LA_ROWS || (act != HS_ACT_NONE && act != HS_ACT_SILU))
     return HS_ERR_UNSUPPORTED;
@@ -220,19 +261,22 @@ HS_EXPORT int hs_lightning_recurrence(float* o, float* state, const float* proj,
     int blocks = n_tokens < 148 * 8 ? n_tokens : 148 * 8;
     cudaError_t e = hs_launch(hs::lightning_act_kernel, dim3(blocks), dim3(256), 0, st,
                               hs_pdl_enabled(), scratch, proj, n_tokens, stride, q_off, k_off,
-                              v_off, hd, hv, act);
+                              v_off, hd, hv, act, D, tok_pos, freq, rot_dims, k_scale);
     if (e != cudaSuccess) return (int)e;
     proj = scratch;
     stride = 2 * hd + hv;
     q_off = 0; k_off = hd; v_off = 2 * hd;
     act = HS_ACT_NONE;
+    rot_dims = 0;           // the rows are turned and scaled already
+    k_scale = 1.0f;
     bulk = 1;
   }
   const size_t smem = (size_t)2 * ntok * (2 * P * hs::LA_PART + cols) * sizeof(float);
   dim3 grid((V + cols - 1) / cols, H, n_requests);
   cudaError_t e = hs_launch(hs::lightning_kernel, grid, dim3(hs::LA_THREADS), smem, st,
                             hs_pdl_enabled(), o, state, proj, decay, req_start, req_len, req_slot,
-                            stride, q_off, k_off, v_off, H, D, V, P, act, ntok, bulk);
+                            stride, q_off, k_off, v_off, H, D, V, P, act, ntok, bulk, tok_pos, freq,
+                            rot_dims, k_scale);
   if (e != cudaSuccess) return (int)e;
   return HS_OK;
 }

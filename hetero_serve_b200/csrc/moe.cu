@@ -194,9 +194,11 @@ moe_route_top_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w,
   }
 }
 
-// act 0: the clamped form above; act 1: silu(g) * u
+// act 0: the clamped form above; act 1: silu(g) * u; act 2: relu(u)^2 (an expert without a gate
+// matrix)
 __device__ __forceinline__ float expert_act(float g, float u, float limit, int act) {
   if (act == 1) return g / (1.0f + expf(-g)) * u;
+  if (act == 2) { const float r = fmaxf(u, 0.f); return r * r; }
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
   return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
@@ -276,7 +278,7 @@ moe_gate_up_rows_kernel(float* __restrict__ y, const TW* __restrict__ h,
   for (int i = 0; i < PER; ++i) {
     const int f = f0 + i * NW;
     const size_t row = ((size_t)e * ff + f) * width;
-    rows[2 * i] = f < ff ? w_gate + row : nullptr;
+    rows[2 * i] = (f < ff && w_gate) ? w_gate + row : nullptr;
     rows[2 * i + 1] = f < ff ? w_up + row : nullptr;
   }
   float res[2 * PER];
@@ -416,7 +418,8 @@ moe_sort_kernel(int* __restrict__ work, int* __restrict__ pair_pos, int* __restr
 // A rows: `a` indexed through row_token when GATHER (the normed rows of the tokens), else the
 // sorted rows themselves.  4 warps, each 32 x 32 of the tile.  Two stages of tiles in shared
 // memory (the next one is copied while this one is used); fragments come through ldmatrix.
-template <int NB, bool GATHER>
+// ACT (with NB = 1): the rows leave activated in bfloat16 as with NB = 2 (an expert without a gate).
+template <int NB, bool GATHER, bool ACT = (NB == 2)>
 __global__ void __launch_bounds__(128)
 moe_tiles_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ a,
                  const __nv_bfloat16* __restrict__ w0, const __nv_bfloat16* __restrict__ w1,
@@ -505,7 +508,7 @@ moe_tiles_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ a,
         for (int q = 0; q < 2; ++q) {
           if (c + q >= ncols) continue;
           const size_t at = (size_t)(row0 + r) * N + n0 + c + q;
-          if (NB == 2)
+          if (ACT)
             ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(
                 expert_act(acc[0][i][j][2 * half + q], acc[NB - 1][i][j][2 * half + q], limit, act));
           else
@@ -584,6 +587,46 @@ HS_EXPORT int hs_moe_route_top(int* sel_idx, float* sel_w, const void* h, const 
 // Scratch of the sorted path for n_tokens x top pairs: ints (work lists, pair positions, row
 // tokens) and bytes of rows (bfloat16 activations, then float32 outputs of the down projection).
 // Returns 0 and zeros when the sorted path does not take the shape.
+namespace hs {
+// the experts of a token id stand in a table [rows, top]; each weighs 1/top
+__global__ void moe_route_table_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w,
+                                       const int* __restrict__ table, int rows,
+                                       const int* __restrict__ tok_ids,
+                                       const int* __restrict__ tok_req,
+                                       const int* __restrict__ feedback, int n_feedback,
+                                       int n_tokens, int top, int E, int* __restrict__ status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * top) return;
+  const int t = i / top, k = i - t * top;
+  if (tok_req[t] < 0) return;
+  int id = tok_ids[t];
+  if (id < 0 && feedback != nullptr && -(id + 1) < n_feedback) id = feedback[-(id + 1)];
+  int e = -1;
+  if (id >= 0 && id < rows) e = table[(size_t)id * top + k];
+  if (e < 0 || e >= E) {
+    atomicOr(status, HS_STATUS_BAD_TOKEN);
+    e = -1;                                   // the expert kernels skip such a pair
+  }
+  sel_idx[i] = e;
+  sel_w[i] = 1.0f / (float)top;
+}
+}  // namespace hs
+
+HS_EXPORT int hs_moe_route_table(int* sel_idx, float* sel_w, const int* table, int rows,
+                                 const int* tok_ids, const int* tok_req, const int* feedback,
+                                 int n_feedback, int n_tokens, int top, int E, int* status,
+                                 void* stream) {
+  if (!sel_idx || !sel_w || !table || !tok_ids || !tok_req || !status) return HS_ERR_ARGUMENT;
+  if (rows <= 0 || top <= 0 || E <= 0) return HS_ERR_UNSUPPORTED;
+  if (n_tokens <= 0) return HS_OK;
+  const int n = n_tokens * top;
+  hs::moe_route_table_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
+      sel_idx, sel_w, table, rows, tok_ids, tok_req, feedback, n_feedback, n_tokens, top, E,
+      status);
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
 HS_EXPORT int hs_moe_sorted_scratch(int n_tokens, int width, int ff, int top, int E, int dtype,
                                     long long* ints, long long* bytes) {
   *ints = 0;
@@ -604,9 +647,9 @@ HS_EXPORT int hs_moe_experts(float* x, float* y, const void* h, const void* w_ga
                              const float* sel_w, const int* tok_req, int n_tokens, int width,
                              int ff, int top, int E, float limit, int act_kind, int dtype, int* ints,
                              void* rows, void* stream) {
-  if (!x || !h || !w_gate || !w_up || !w_down || !sel_idx || !sel_w || !tok_req)
+  if (!x || !h || !w_up || !w_down || !sel_idx || !sel_w || !tok_req || (!w_gate && act_kind != 2))
     return HS_ERR_ARGUMENT;
-  if (width <= 0 || ff <= 0 || top <= 0 || E <= 0 || act_kind < 0 || act_kind > 1) return HS_ERR_UNSUPPORTED;
+  if (width <= 0 || ff <= 0 || top <= 0 || E <= 0 || act_kind < 0 || act_kind > 2) return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (ints && rows) {
@@ -624,9 +667,14 @@ HS_EXPORT int hs_moe_experts(float* x, float* y, const void* h, const void* w_ga
         work, pair_pos, row_token, sel_idx, tok_req, n_tokens, top, E, max_tiles);
     HS_LAUNCH_CHECK();
     const __nv_bfloat16* hb = (const __nv_bfloat16*)h;
-    hs::moe_tiles_kernel<2, true><<<dim3(max_tiles, (ff + hs::TN - 1) / hs::TN), 128, 0, st>>>(
-        act, hb, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, work, row_token, E,
-        max_tiles, ff, width, limit, act_kind);
+    if (w_gate)
+      hs::moe_tiles_kernel<2, true><<<dim3(max_tiles, (ff + hs::TN - 1) / hs::TN), 128, 0, st>>>(
+          act, hb, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, work, row_token, E,
+          max_tiles, ff, width, limit, act_kind);
+    else
+      hs::moe_tiles_kernel<1, true, true><<<dim3(max_tiles, (ff + hs::TN - 1) / hs::TN), 128, 0, st>>>(
+          act, hb, (const __nv_bfloat16*)w_up, nullptr, work, row_token, E, max_tiles, ff, width,
+          limit, act_kind);
     HS_LAUNCH_CHECK();
     hs::moe_tiles_kernel<1, false><<<dim3(max_tiles, (width + hs::TN - 1) / hs::TN), 128, 0, st>>>(
         down, act, (const __nv_bfloat16*)w_down, nullptr, work, row_token, E, max_tiles, width,

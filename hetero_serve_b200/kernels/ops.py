@@ -34,7 +34,7 @@ def learned_constants(act: str, values) -> tuple[float, float]:
         raise KernelError(f"activation {act!r} with {len(values)} numbers not taken")
     sp = lambda v: math.log1p(math.exp(-abs(v))) + max(v, 0.0)      # softplus
     return sp(values[0]), 0.5 + sp(values[1])
-EXPERT_ACTIVATIONS = {"clamped": 0, "silu": 1}
+EXPERT_ACTIVATIONS = {"clamped": 0, "silu": 1, "relu2": 2}
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
 
@@ -222,7 +222,17 @@ def _declare(lib) -> None:
                                 I, P, P, P, P],
         "hs_biased_attention_prefill": [P, P, P, P, P, P, I, P, P, I, P, I, I, I, I, I, I, I, I,
                                         F, F, I, I, P, P],
-        "hs_lightning_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
+        "hs_lightning_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P, P, I,
+                                    F, P],
+        "hs_token_shift_mix": [P, P, P, P, I, I, P, P, P, P, I, I, I, I, P],
+        "hs_timemix_decay": [P, P, P, P, I, I, I, P],
+        "hs_timemix_recurrence": [P, P, I, P, P, P, P, P, P, P, P, I, I, I, I, P],
+        "hs_head_norm_gate": [P, P, P, P, I, I, I, I, I, F, I, F, I, P],
+        "hs_gather_mul": [P, P, P, I, I, P, P, P, I, I, I, I, I, I, P, P],
+        "hs_moe_route_table": [P, P, P, I, P, P, P, I, I, I, I, P, P],
+        "hs_span_prepare": [P, P, P, I, I, I, I, P, I, I, P, P, I, I, I, I, I, I, F, I, I, I, P, P],
+        "hs_span_attention": [P, P, P, P, I, I, P, P, P, P, I, I, F, I, I, I, I, I, I, I, F, I, I,
+                              I, P, P, P, P],
         "hs_layernorm_add": [P, P, P, P, F, P, P, P, F, I, I, I, P],
         "hs_learned_act_xielu": [P, P, ctypes.c_longlong, F, F, I, P],
         "hs_scale_softcap": [P, ctypes.c_longlong, F, F, P],
@@ -326,6 +336,7 @@ class CudaOps:
         self.latent_mma = True      # prompt portions of latent attention on the tensor cores
         self.biased_mma = True      # prompt portions of the biased chunk attention likewise
         self.pooled_mma = True      # ... and of the attention over a window and pooled blocks
+        self.span_mma = True        # ... and of the attention with a distance slope and a window
         self.folds_pooled_means = True   # pooled_prepare takes the companion pool (single tokens)
         self.lightning_bulk_rows = 64   # from this many tokens a step on, lightning attention
         #                                 activates its rows in a pass of their own
@@ -1256,7 +1267,8 @@ class CudaOps:
                     act="clamped"):
         """x += sum over a token's chosen experts of weight * W_down act(W_gate h, W_up h) with
         act(g, u) = min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, +-limit) + 1)
-        (``act="clamped"``) or silu(g) * u (``act="silu"``, no limit).
+        (``act="clamped"``) or silu(g) * u (``act="silu"``, no limit), or W_down relu(W_up h)^2
+        for experts without a gate matrix (``act="relu2"``, ``w_gate`` None).
         Expert matrices stacked as stored: gate / up [E, ff, width], down [E, width, ff]; ``y``
         is float32 scratch [T * top, ff].  Many pairs in bfloat16 are sorted by expert on the
         device and run as tiles on the tensor cores; few pairs, and float32, as one
@@ -1264,9 +1276,12 @@ class CudaOps:
         _want(x, "x", torch.float32, 2)
         _want(y, "y", torch.float32, 2)
         _want(h, "h", _FLOATS, 2)
+        if (w_gate is None) != (act == "relu2"):
+            raise KernelError("moe_experts: experts have a gate matrix unless act is 'relu2'")
         for t, nm in ((w_gate, "w_gate"), (w_up, "w_up"), (w_down, "w_down")):
-            _want(t, nm, h.dtype, 3)
-        E, ff, width = w_gate.shape
+            if t is not None:
+                _want(t, nm, h.dtype, 3)
+        E, ff, width = w_up.shape
         T, top = sel_idx.shape
         if tuple(w_up.shape) != (E, ff, width) or tuple(w_down.shape) != (E, width, ff) \
                 or h.shape[1] != width or x.shape[1] != width or y.shape[0] < T * top \
@@ -1504,11 +1519,14 @@ class CudaOps:
 
     # -- linear attention with a decay per head ---------------------------------------------
     def lightning_recurrence(self, o, state, proj, decay, req_start, req_len, req_slot, *, q_off,
-                             k_off, v_off, heads, dim, vdim, act="silu"):
+                             k_off, v_off, heads, dim, vdim, act="silu", tok_pos=None, freq=None,
+                             rot_dims=0, k_scale=1.0):
         """Per request and head, token after token on the float32 state S [dim, vdim] of the
         request's slot: S <- decay[h] S + k v^T; o = S^T q, with q, k, v = act(columns of the
         float32 projection rows ``proj``), laid out head by head from ``q_off``, ``k_off``,
-        ``v_off``.  ``o`` is float32 [T, heads * vdim]."""
+        ``v_off``.  ``o`` is float32 [T, heads * vdim].  With ``freq`` (float32 [rot_dims / 2])
+        q and k are turned by ``tok_pos`` on their first ``rot_dims`` numbers (number i pairs
+        with i + rot_dims / 2) before they are used; k is multiplied by ``k_scale``."""
         _want(o, "o", torch.float32, 2)
         _want(proj, "proj", torch.float32, 2)
         _want(state, "state", torch.float32)
@@ -1521,6 +1539,14 @@ class CudaOps:
             raise KernelError("lightning_recurrence: the columns exceed the projection's row")
         if act not in ("none", "silu"):
             raise KernelError(f"lightning_recurrence: activation {act!r} not taken")
+        if freq is None:
+            rot_dims = 0
+        elif rot_dims:
+            _want(freq, "freq", torch.float32, 1)
+            _want(tok_pos, "tok_pos", torch.int32, 1)
+            if rot_dims % 2 or rot_dims > dim or freq.shape[0] < rot_dims // 2 \
+                    or tok_pos.shape[0] < o.shape[0]:
+                raise KernelError("lightning_recurrence: the rotated extent does not fit")
         # steps of many tokens: the activations in a pass of their own into compact rows, which
         # the recurrence then streams 16 bytes at a time (the same bits either way)
         T = o.shape[0]
@@ -1532,7 +1558,9 @@ class CudaOps:
         _check(self.lib.hs_lightning_recurrence(
             _ptr(o), _ptr(state), _ptr(proj), _ptr(decay), _ptr(req_start), _ptr(req_len),
             _ptr(req_slot), req_start.shape[0], T, proj.shape[1], int(q_off), int(k_off),
-            int(v_off), heads, dim, vdim, ACTIVATIONS[act], _ptr(scratch), self._stream()),
+            int(v_off), heads, dim, vdim, ACTIVATIONS[act], _ptr(scratch),
+            _ptr(tok_pos) if rot_dims else None, _ptr(freq) if rot_dims else None, int(rot_dims),
+            float(k_scale), self._stream()),
             f"lightning_recurrence(dim={dim},vdim={vdim})")
 
     # -- norms behind a sublayer, a learned activation, capped logits -----------------------
@@ -1751,6 +1779,212 @@ class CudaOps:
             D, V, int(window), int(block), float(scale), int(page_size), _DT[pool.dtype],
             _DT[out.dtype], _ptr(listed), _ptr(head), _ptr(status), self._stream()),
             f"pooled_attention(head_dim={D},value_dim={V})")
+
+    # -- time mixing, head norms, token-indexed tables ---------------------------------------
+    def token_shift_mix(self, out, x, mu, state, tok_req, req_start, req_len, req_slot, *,
+                        state_offset):
+        """out[s, t] = x[t] + (x'[t] - x[t]) * mu[s] for every stream s (``mu`` float32
+        [streams, width]), x' being the row before in the request; for a request's first row of
+        the step it is the float32 row kept at ``state[slot, state_offset:]``, which then
+        receives the step's last row of the request."""
+        _want(out, "out", _FLOATS, 3)
+        _want(x, "x", out.dtype, 2)
+        _want(mu, "mu", torch.float32, 2)
+        _want(state, "state", torch.float32, 2)
+        S, T, W = out.shape
+        if x.shape[0] < T or x.shape[1] != W or tuple(mu.shape) != (S, W) \
+                or state_offset + W > state.shape[1]:
+            raise KernelError("token_shift_mix: shapes do not fit")
+        self.launches += 1
+        _check(self.lib.hs_token_shift_mix(
+            _ptr(out), _ptr(x), _ptr(mu), _ptr(state), state.shape[1], int(state_offset),
+            _ptr(tok_req), _ptr(req_start), _ptr(req_len), _ptr(req_slot), T, W, S,
+            _DT[out.dtype], self._stream()), "token_shift_mix")
+
+    def timemix_decay(self, out, low, w2, w0):
+        """out[t, c] = exp(-exp(sum_j w2[c, j] tanh(low[t, j]) + w0[c])), all float32."""
+        _want(out, "out", torch.float32, 2)
+        _want(low, "low", torch.float32, 2)
+        _want(w2, "w2", torch.float32, 2)
+        _want(w0, "w0", torch.float32, 1)
+        T, C = out.shape
+        rank = low.shape[1]
+        if low.shape[0] < T or tuple(w2.shape) != (C, rank) or w0.shape[0] != C:
+            raise KernelError("timemix_decay: shapes do not fit")
+        self.launches += 1
+        _check(self.lib.hs_timemix_decay(_ptr(out), _ptr(low), _ptr(w2), _ptr(w0), T, C, rank,
+                                         self._stream()), f"timemix_decay(rank={rank})")
+
+    def timemix_recurrence(self, o, state, r, k, v, w, u, req_start, req_len, req_slot, *, heads,
+                           dim):
+        """Per request and head, token after token on the float32 state S [dim, dim] at the
+        start of the request's slot: o = (S + diag(u) k v^T)^T r, then S <- diag(w) S + k v^T.
+        r, k, v, w, o: float32 [T, heads * dim]; u: float32 [heads * dim]."""
+        T = o.shape[0]
+        for t, nm in ((o, "o"), (r, "r"), (k, "k"), (v, "v"), (w, "w")):
+            _want(t, nm, torch.float32, 2)
+            if t.shape[0] < T or t.shape[1] != heads * dim:
+                raise KernelError(f"timemix_recurrence: {nm} is [T, heads * dim]")
+        _want(u, "u", torch.float32, 1)
+        _want(state, "state", torch.float32, 2)
+        if u.shape[0] != heads * dim or state.shape[1] < heads * dim * dim:
+            raise KernelError("timemix_recurrence: u / state do not fit the sizes")
+        self.launches += 1
+        _check(self.lib.hs_timemix_recurrence(
+            _ptr(o), _ptr(state), state.shape[1], _ptr(r), _ptr(k), _ptr(v), _ptr(w), _ptr(u),
+            _ptr(req_start), _ptr(req_len), _ptr(req_slot), req_start.shape[0], T, heads, dim,
+            self._stream()), f"timemix_recurrence(dim={dim})")
+
+    def head_norm_gate(self, out, o, weight, gate, *, gate_offset, heads, dim, eps,
+                       gate_act="silu", out_scale=1.0):
+        """out[t, h] = o[t, h] / rms(o[t, h]) (* weight) * act(gate columns) * out_scale for
+        every head h of ``dim`` numbers; ``gate`` is float32 [T, *] with the head's columns from
+        ``gate_offset`` on, ``gate_act`` silu or sigmoid; weight and gate may be None."""
+        _want(out, "out", _FLOATS, 2)
+        _want(o, "o", torch.float32, 2)
+        T = out.shape[0]
+        if out.shape[1] != heads * dim or o.shape[1] != heads * dim or o.shape[0] < T:
+            raise KernelError("head_norm_gate: out / o are [T, heads * dim]")
+        if weight is not None:
+            _want(weight, "weight", torch.float32, 1)
+            if weight.shape[0] != heads * dim:
+                raise KernelError("head_norm_gate: one weight per number")
+        g_stride = 0
+        if gate is not None:
+            _want(gate, "gate", torch.float32, 2)
+            g_stride = gate.shape[1]
+            if gate.shape[0] < T or gate_offset + heads * dim > g_stride:
+                raise KernelError("head_norm_gate: the gate columns exceed the gate's row")
+        if gate_act not in ("silu", "sigmoid"):
+            raise KernelError(f"head_norm_gate: gate activation {gate_act!r} not taken")
+        self.launches += 1
+        _check(self.lib.hs_head_norm_gate(
+            _ptr(out), _ptr(o), _ptr(weight), _ptr(gate), g_stride, int(gate_offset), T, heads,
+            dim, float(eps), int(gate_act == "silu"), float(out_scale), _DT[out.dtype],
+            self._stream()), f"head_norm_gate(dim={dim})")
+
+    def gather_mul(self, out, g, table, tok_ids, tok_req, *, col_offset, feedback=None):
+        """out[t, c] = g[t, c] * table[token[t], col_offset + c] (``g`` float32, ``out`` and
+        ``table`` in the compute type); a token id -(s + 1) stands for ``feedback[s]``."""
+        _want(out, "out", _FLOATS, 2)
+        _want(g, "g", torch.float32, 2)
+        _want(table, "table", out.dtype, 2)
+        T, dim = out.shape
+        if g.shape[0] < T or g.shape[1] != dim or col_offset + dim > table.shape[1]:
+            raise KernelError("gather_mul: shapes do not fit")
+        self.launches += 1
+        _check(self.lib.hs_gather_mul(
+            _ptr(out), _ptr(g), _ptr(table), table.shape[0], table.shape[1], _ptr(tok_ids),
+            _ptr(tok_req), _ptr(feedback), 0 if feedback is None else feedback.shape[0], T, dim,
+            int(col_offset), _DT[out.dtype], _DT[table.dtype], _ptr(self._status_of(tok_ids)),
+            self._stream()), "gather_mul")
+
+    def moe_route_table(self, sel_idx, sel_w, table, tok_ids, tok_req, *, top, feedback=None,
+                        experts=None):
+        """sel_idx[t] = table[token[t], :top] (int32 [rows, top]), sel_w = 1 / top."""
+        _want(sel_idx, "sel_idx", torch.int32, 2)
+        _want(sel_w, "sel_w", torch.float32, 2)
+        _want(table, "table", torch.int32, 2)
+        if table.shape[1] != top or sel_idx.shape[1] != top or sel_w.shape[1] != top:
+            raise KernelError("moe_route_table: shapes do not fit")
+        self.launches += 1
+        _check(self.lib.hs_moe_route_table(
+            _ptr(sel_idx), _ptr(sel_w), _ptr(table), table.shape[0], _ptr(tok_ids), _ptr(tok_req),
+            _ptr(feedback), 0 if feedback is None else feedback.shape[0], sel_idx.shape[0], top,
+            int(experts) if experts else 0x7fffffff, _ptr(self._status_of(tok_ids)),
+            self._stream()), f"moe_route_table(top={top})")
+
+    def _status_of(self, like):
+        """A status word for kernels whose part hands none in: the engine's own when the runner
+        has set it (``self.status``), else a private one."""
+        st = getattr(self, "status", None)
+        if st is None:
+            st = self._scratch_buffer("own_status", 1, torch.int32)
+        return st
+
+    # -- attention with a distance slope, a window and kept first tokens ---------------------
+    def span_prepare(self, q_out, pool, proj, table, tok_pos, tok_req, *, n_heads, n_kv_heads,
+                     head_dim, value_dim, q_off, k_off, v_off, qk_norm, eps, writes, page_size,
+                     status):
+        """From float32 projection rows: q (columns from ``q_off``) to ``q_out`` (float32), and
+        with ``writes`` the row [k | v] of every key/value head into the token's page; with
+        ``qk_norm`` q and k are divided by their root mean square per head first.  ``v_off``
+        None: the values are the keys as projected (before the norm).  ``pool`` is
+        [pages, kv_heads, page_size, head_dim + value_dim]."""
+        _want(q_out, "q_out", torch.float32, 2)
+        _want(proj, "proj", torch.float32, 2)
+        _want(pool, "pool", _FLOATS)
+        _want(table, "table", torch.int32, 2)
+        H, G, D, V = n_heads, n_kv_heads, head_dim, value_dim
+        if q_out.shape[1] != H * D or proj.shape[0] < q_out.shape[0]:
+            raise KernelError("span_prepare: the rows do not fit the heads")
+        if writes and k_off is None:
+            raise KernelError("span_prepare: a layer that writes its rows has key columns")
+        self.launches += 1
+        _check(self.lib.hs_span_prepare(
+            _ptr(q_out), _ptr(pool), _ptr(proj), proj.shape[1], int(q_off),
+            -1 if k_off is None else int(k_off), -1 if v_off is None else int(v_off), _ptr(table),
+            table.shape[1], pool.numel() // (G * page_size * (D + V)), _ptr(tok_pos),
+            _ptr(tok_req), q_out.shape[0], H, G, D, V, int(bool(qk_norm)), float(eps),
+            int(page_size), int(bool(writes)), _DT[pool.dtype], _ptr(status), self._stream()),
+            f"span_prepare(head_dim={D},value_dim={V})")
+
+    def span_attention(self, out, q, pool, table, tok_pos, tok_req, *, n_heads, n_kv_heads,
+                       head_dim, value_dim, scale, slopes, window, keep_first, gate, gate_offset,
+                       out_scale, page_size, status, plan=None):
+        """Per token at position i and query head h: softmax over the keys j <= i with
+        i - j < window (0: all) or j < keep_first of (q . k) * scale - slopes[h] * (i - j)
+        (``slopes`` float32 [heads] or None); the head's output times sigmoid(gate[t,
+        gate_offset + h * value_dim + e]) (``gate`` float32 [T, *] or None) times
+        ``out_scale``.  With the step's ``plan`` and a bfloat16 cache the plan's tiles (prompt
+        portions) run on the tensor cores and its single-query tokens on the CUDA cores;
+        without a plan, in float32 and for sizes the tile kernel does not take every token
+        runs on the CUDA cores."""
+        _want(out, "out", _FLOATS, 2)
+        _want(q, "q", torch.float32, 2)
+        _want(pool, "pool", out.dtype)
+        _want(table, "table", torch.int32, 2)
+        H, G, D, V = n_heads, n_kv_heads, head_dim, value_dim
+        T = out.shape[0]
+        if out.shape[1] != H * V or q.shape[1] != H * D or q.shape[0] < T:
+            raise KernelError("span_attention: the rows do not fit the heads")
+        if slopes is not None:
+            _want(slopes, "slopes", torch.float32, 1)
+            if slopes.shape[0] != H:
+                raise KernelError("span_attention: one slope per head")
+        g_stride = 0
+        if gate is not None:
+            _want(gate, "gate", torch.float32, 2)
+            g_stride = gate.shape[1]
+            if gate.shape[0] < T or gate_offset + H * V > g_stride:
+                raise KernelError("span_attention: the gate columns exceed the gate's row")
+        per_page = G * page_size * (D + V)
+        num_pages = pool.numel() // per_page
+        listed = head = None
+        if (plan is not None and plan.tile_cap > 0 and out.dtype == torch.bfloat16
+                and self.tensor_cores and self.span_mma and plan.n_rows >= T
+                and hasattr(self.lib, "hs_span_attention_prefill")):
+            d = plan.data
+            code = self.lib.hs_span_attention_prefill(
+                _ptr(out), _ptr(q), _ptr(pool), _ptr(table), table.shape[1], num_pages,
+                _ptr(d[4 + plan_decode_ints(plan.n_rows):]), _ptr(d), plan.tile_cap,
+                _ptr(self._scratch_buffer("span_counter", 1, torch.int32)), _ptr(slopes),
+                _ptr(gate), g_stride, int(gate_offset), float(out_scale), H, G, D, V, int(window),
+                int(keep_first), float(scale), int(page_size), _ptr(status), self._stream())
+            if code != -1:
+                _check(code, f"span_attention_prefill(head_dim={D},value_dim={V})")
+                self.launches += 1
+                if plan.decode_cap == 0:
+                    return
+                listed, head = d[4:], d         # the CUDA-core kernel takes the single tokens
+                T = plan.decode_cap
+        self.launches += 1
+        _check(self.lib.hs_span_attention(
+            _ptr(out), _ptr(q), _ptr(pool), _ptr(table), table.shape[1], num_pages, _ptr(tok_pos),
+            _ptr(tok_req), _ptr(slopes), _ptr(gate), g_stride, int(gate_offset), float(out_scale),
+            T, H, G, D, V, int(window), int(keep_first), float(scale), int(page_size),
+            _DT[pool.dtype], _DT[out.dtype], _ptr(listed), _ptr(head), _ptr(status),
+            self._stream()), f"span_attention(head_dim={D},value_dim={V})")
 
     # -- sampling ---------------------------------------------------------------
     def argmax(self, out, logits):

@@ -122,7 +122,7 @@ class RoutedExperts(FeedForward):
             ops.linear(z, h, self.w_router_lp)
         if self.scoring == "table":
             ops.moe_route_table(idx, wts, self.w_router, ctx.tok_ids, ctx.tok_req, top=self.top,
-                                feedback=ctx.feedback)
+                                feedback=ctx.feedback, experts=self.E)
         elif self.scoring == "softmax_top":
             ops.moe_route_top(idx, wts, h, self.w_router, self.b_router, ctx.tok_req,
                               top=self.top, z=z)

@@ -638,7 +638,8 @@ class PlainOps:
             e = table[self._token(tok_ids, t, feedback), col_offset:col_offset + dim]
             out[t] = (g[t].to(self.cd) * e.to(self.cd)).to(out.dtype)
 
-    def moe_route_table(self, sel_idx, sel_w, table, tok_ids, tok_req, *, top, feedback=None):
+    def moe_route_table(self, sel_idx, sel_w, table, tok_ids, tok_req, *, top, feedback=None,
+                        experts=None):
         for t in range(sel_idx.shape[0]):
             if int(tok_req[t]) < 0:
                 continue
