@@ -134,3 +134,20 @@ def roritar_case(request, roritar_cases):
 def roritar_planted(tmp_path_factory):
     import roritar_cases as rc
     return rc.planted_case(tmp_path_factory)
+
+
+@pytest.fixture(scope="session")
+def mafuzen_cases(tmp_path_factory):
+    import mafuzen_cases as mc
+    return mc.make_cases(tmp_path_factory)
+
+
+@pytest.fixture(params=["case_a", "case_b"])
+def mafuzen_case(request, mafuzen_cases):
+    return mafuzen_cases[request.param]
+
+
+@pytest.fixture(scope="session")
+def mafuzen_planted(tmp_path_factory):
+    import mafuzen_cases as mc
+    return {which: mc.planted_case(tmp_path_factory, which) for which in mc.PLANTED}

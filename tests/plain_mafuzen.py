@@ -78,6 +78,7 @@ def retention(m, w, pre, h, eps):
     v = (h @ w[pre + "v"].T).view(T, H, V)
     gate = silu(h @ w[pre + "g"].T)
     rot = m.get("rot")
+    decay = m["decay"] if isinstance(m["decay"], (list, tuple)) else [m["decay"]] * H
     o = torch.zeros(T, H, V, dtype=F64)
     for hd in range(H):
         S = torch.zeros(D, V, dtype=F64)
@@ -87,7 +88,7 @@ def retention(m, w, pre, h, eps):
                 qt = rotate_halves(qt, t, rot["base"], rot["dims"])
                 kt = rotate_halves(kt, t, rot["base"], rot["dims"])
             kt = kt * D ** -0.5
-            S = m["decay"][hd] * S + torch.outer(kt, v[t, hd])
+            S = decay[hd] * S + torch.outer(kt, v[t, hd])
             o[t, hd] = S.T @ qt
     o = unit_rms(o, eps).reshape(T, H * V)
     return (o * gate) @ w[pre + "o"].T
@@ -142,8 +143,9 @@ def window_attention(m, w, pre, h, eps):
     q = (h @ w[pre + "q"].T).view(T, H, D)
     k = (h @ w[pre + "k"].T).view(T, G, D)
     v = k
+    mask = m.get("mask") or {"size": 0}                 # no mask: every earlier token is seen
     o = softmax_attention(unit_rms(q, eps), unit_rms(k, eps), v, m["scale"], None,
-                          m["mask"]["size"], m["mask"].get("keep_first", 0))
+                          mask["size"], mask.get("keep_first", 0))
     gate = torch.sigmoid(h @ w[pre + "g"].T)
     return (o.reshape(T, H * D) * gate) @ w[pre + "o"].T
 
