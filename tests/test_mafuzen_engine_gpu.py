@@ -1,0 +1,253 @@
+"""Mafuzen through the engine on the GPU: the step function, the paged cache with a windowed
+group that keeps its first pages and an entry that three layers read, the state slots and the
+CUDA kernels against the plain implementation (tests/plain_mafuzen.py), in both precisions;
+then greedy generation through the Python entry point and its scheduler."""
+
+import io
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_mafuzen
+import mafuzen_cases as rc
+import traces
+from hetero_serve_b200.engine.loading import load_model
+from hetero_serve_b200.engine.replay import replay
+from hetero_serve_b200.engine.step import Runner, StepEntry
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+# relative root-mean-square error of a row of logits: float32 sums of a few hundred terms;
+# bfloat16 rounds the rows the projections read and the cache rows to 8 bits
+TOL = {"float32": 3e-5, "bfloat16": 6e-2}
+
+
+def _bound(errs, dtype):
+    """float32: the largest error.  bfloat16: nineteen rows in twenty and three times the
+    median; a squared ReLU and unit norms of small outputs make single rows far off while
+    nothing is wrong."""
+    errs = sorted(errs)
+    if dtype == "float32":
+        return errs[-1]
+    return max(errs[int(0.95 * (len(errs) - 1))], 3 * errs[len(errs) // 2]) if len(errs) > 4 \
+        else errs[len(errs) // 2]
+
+
+def _replay(case, dtype, steps, tmp_path, max_tokens, **kw):
+    out = tmp_path / f"out_{dtype}"
+    out.mkdir(exist_ok=True)
+    assert replay(model_dir=case.dir, dtype=dtype, out_dir=out, max_tokens=max_tokens,
+                  lines=traces.lines_of(steps), report=io.StringIO(), device=DEV, **kw) == 0
+    return out
+
+
+def _worst(case, dtype, out, index, reqs):
+    got = traces.collect(out, index, case.vocab)
+    errs = sorted(((rc.rms_error(torch.as_tensor(row), case.logits(reqs[rid], dtype)[p]),
+                    (rid, p)) for (rid, p), row in got.items()), reverse=True)
+    return _bound([e for e, _ in errs], dtype), errs[0][1], len(errs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("driver", ["whole", "tail", "portions"])
+def test_cuts_agree_with_the_plain_model(mafuzen_case, tmp_path, dtype, driver):
+    reqs = {f"r{i}": mafuzen_case.tokens(n, 150 + i) for i, n in enumerate((1, 2, 23, 70, 131))}
+    if driver == "whole":
+        steps, index = traces.whole(reqs)
+    elif driver == "tail":
+        steps, index = traces.tail_one_by_one(reqs, tail=50)
+    else:
+        steps, index = traces.portions(reqs, sizes=(24, 7, 2, 16, 3, 2, 31, 5, 2, 9))
+    out = _replay(mafuzen_case, dtype, steps, tmp_path, max_tokens=192)
+    err, where, n = _worst(mafuzen_case, dtype, out, index, reqs)
+    assert n > 4 and err < TOL[dtype], (err, where)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_reuse_pages_and_slots(mafuzen_case, tmp_path, dtype):
+    reqs = {f"r{i}": mafuzen_case.tokens(n, 170 + i) for i, n in
+            enumerate((90, 9, 64, 23, 70, 3, 55, 31, 2))}
+    steps, index, peak = traces.mixed(reqs, seed=2)
+    out = _replay(mafuzen_case, dtype, steps, tmp_path, max_tokens=peak, max_requests=4)
+    err, where, n = _worst(mafuzen_case, dtype, out, index, reqs)
+    assert n > 40 and err < TOL[dtype], (err, where)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_wide_sizes_and_long_prompts(mafuzen_cases, tmp_path, dtype):
+    """Sizes the tensor-core linears, the tile attention and the 16-byte cache reads take,
+    prompts longer than the window, stored in bfloat16."""
+    case = mafuzen_cases["case_c"]
+    reqs = {"a": case.tokens(300, 301), "b": case.tokens(150, 302), "c": case.tokens(9, 303)}
+    steps, index = traces.whole(reqs)
+    out = _replay(case, dtype, steps, tmp_path, max_tokens=384)
+    err, where, n = _worst(case, dtype, out, index, reqs)
+    assert n > 200 and err < TOL[dtype], (err, where)
+    more = {"d": case.tokens(260, 304)}
+    steps, index = traces.portions(more, sizes=(70, 2, 70, 1, 17))
+    out = _replay(case, dtype, steps, tmp_path, max_tokens=320)
+    err, where, n = _worst(case, dtype, out, index, more)
+    assert err < TOL[dtype], (err, where)
+
+
+def _runner(case, dtype="float32", pages=16, slots=4, **kw):
+    model, _ = load_model(case.dir, dtype, DEV)
+    return Runner(model, num_pages=pages, page_size=16, max_requests=slots, dtype=model.dtype,
+                  device=DEV, **kw)
+
+
+def test_a_request_alone_and_in_a_batch(mafuzen_case):
+    """The logits of a request do not depend on its neighbours in the batch, nor on the slot
+    and pages it got: in float32 they are the same bits."""
+    case = mafuzen_case
+    a, b, c = case.tokens(45, 1), case.tokens(20, 2), case.tokens(33, 3)
+    alone = _runner(case)
+    want = alone.step([StepEntry("a", a[:30], want=[29])]).logits.clone()
+    want2 = alone.step([StepEntry("a", a[30:], want=[0, 14])]).logits.clone()
+    rn = _runner(case)
+    rn.step([StepEntry("c", c)])                  # takes the first slot and pages
+    got = rn.step([StepEntry("b", b[:7]), StepEntry("a", a[:30], want=[29]),
+                   StepEntry("c", [5])]).logits.clone()
+    rn.close("c")
+    got2 = rn.step([StepEntry("a", a[30:], want=[0, 14]), StepEntry("b", b[7:])]).logits
+    assert torch.equal(got, want) and torch.equal(got2, want2)
+    assert rc.rms_error(got2[1].cpu(), case.logits(a)[44]) < TOL["float32"]
+
+
+def test_freed_slots_and_pages_start_clean(mafuzen_cases):
+    case = mafuzen_cases["case_a"]
+    rn = _runner(case, pages=8, slots=1)
+    for seed, n in ((4, 100), (5, 41), (6, 110)):
+        t = case.tokens(n, seed)
+        rn.step([StepEntry("x", t[:n // 2])])
+        res = rn.step([StepEntry("x", t[n // 2:], want=[n - n // 2 - 1])])
+        assert rc.rms_error(res.logits[0].cpu(), case.logits(t)[n - 1]) < TOL["float32"], seed
+        rn.close("x")
+    rn.manager.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("how", ["whole", "alone", "portions"])
+def test_the_edges_of_the_window_and_of_the_first_tokens(mafuzen_planted, dtype, how):
+    """One key that takes nearly all of the softmax when it is visible, asked for from every
+    distance around the window's edge, as a first token that is kept and as the next one that
+    is not, from far away, and with the key on a page's last and first row."""
+    case = mafuzen_planted["window"]
+    rn = _runner(case, dtype, pages=40, slots=2)
+    k = 0
+    for at in (0, 4, 5, 15, 16):
+        for d in (1, 11, 12, 13, 14, 15, 16, 17, 31, 32, 33, 150, 400):
+            t = rc.planted_tokens(case, at, at + d + 1, 100 + d)
+            n, rid = len(t), f"q{k}"
+            k += 1
+            if how == "whole":
+                res = rn.step([StepEntry(rid, t, want=[n - 1])])
+            elif how == "alone":
+                rn.step([StepEntry(rid, t[:-1])])
+                res = rn.step([StepEntry(rid, t[-1:], want=[0])])
+            else:
+                cut = max(1, n - 2)
+                for a in range(0, cut, 7):
+                    rn.step([StepEntry(rid, t[a:min(cut, a + 7)])])
+                res = rn.step([StepEntry(rid, t[cut:], want=[n - cut - 1])])
+            rn.close(rid)
+            err = rc.rms_error(res.logits[-1].cpu(), case.logits(t, dtype)[-1])
+            assert err < TOL[dtype], (at, d, err)
+    rn.manager.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("how", ["whole", "alone", "tiles"])
+def test_a_far_key_under_the_slope(mafuzen_planted, dtype, how):
+    """One key among hundreds, at the start, at a page's edge and one position back; ``tiles``
+    brings the last 140 tokens as one portion (query tiles that start inside the prompt)."""
+    case = mafuzen_planted["slope"]
+    rn = _runner(case, dtype, pages=64, slots=2)
+    for k, (at, n) in enumerate(((0, 700), (15, 333), (16, 410), (100, 102), (1, 300))):
+        t = rc.planted_tokens(case, at, n, 7 + at)
+        rid = f"q{k}"
+        if how == "whole":
+            res = rn.step([StepEntry(rid, t, want=[n - 1])])
+        elif how == "alone":
+            rn.step([StepEntry(rid, t[:-1])])
+            res = rn.step([StepEntry(rid, t[-1:], want=[0])])
+        else:
+            cut = max(1, n - 140)
+            rn.step([StepEntry(rid, t[:cut])])
+            res = rn.step([StepEntry(rid, t[cut:], want=[n - cut - 1])])
+        rn.close(rid)
+        err = rc.rms_error(res.logits[-1].cpu(), case.logits(t, dtype)[-1])
+        assert err < TOL[dtype], (at, n, err)
+
+
+def test_long_decoding(mafuzen_cases):
+    """Single-token steps across many window and page borders, the pages behind the window
+    going back to the pool while the page of the first tokens stays."""
+    case = mafuzen_cases["case_a"]
+    t = case.tokens(280, 9)
+    rn = _runner(case, pages=20, slots=1)
+    rn.step([StepEntry("d", t[:12])])
+    want = case.logits(t)
+    for i in range(12, 280):
+        res = rn.step([StepEntry("d", [t[i]], want=[0])])
+        if i % 5 in (0, 4) or i % 16 == 0 or i in (20, 21, 33, 34, 35) or i > 270:
+            assert rc.rms_error(res.logits[0].cpu(), want[i]) < TOL["float32"], i
+    rn.manager.check()
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_captured_steps_equal_eager_steps(mafuzen_cases, dtype):
+    """The same steps through CUDA graphs (sizes rounded up to a class, padding rows, the state
+    restored after the run that precedes a capture) and launched one by one."""
+    case = mafuzen_cases["case_c"]
+    a, b = case.tokens(140, 401), case.tokens(30, 402)
+    eager, graphs = _runner(case, dtype, pages=24), _runner(case, dtype, pages=24, cuda_graphs=True)
+    plan = [[("a", a[:100], [99])], [("a", a[100:120], [0, 19]), ("b", b[:1], [0])],
+            [("a", a[120:121], [0]), ("b", b[1:2], [0])], [("a", a[121:122], [0]), ("b", b[2:3], [0])],
+            [("a", a[122:140], [17]), ("b", b[3:4], [0])], [("a2", a[:100], [99])]]
+    for step in plan:
+        want = eager.step([StepEntry(r, t, w) for r, t, w in step]).logits.clone()
+        got = graphs.step([StepEntry(r, t, w) for r, t, w in step]).logits.clone()
+        for i in range(want.shape[0]):
+            assert rc.rms_error(got[i].cpu(), want[i].cpu()) < (2e-2 if dtype == "bfloat16" else 1e-5), step[0][0]
+    assert rc.rms_error(want[0].cpu(), case.logits(a, dtype)[99]) < TOL[dtype] * 3
+
+
+def _greedy(case, prompt, n):
+    toks, out, margins = list(prompt), [], []
+    for _ in range(n):
+        row = plain_mafuzen.forward(case.config, case.plain, toks)[-1]
+        top = torch.topk(row, 2).values
+        margins.append(float(top[0] - top[1]))
+        out.append(int(row.argmax()))
+        toks.append(out[-1])
+    return out, margins
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_through_the_entry_point(mafuzen_case, graphs):
+    """Prompts of unequal length, cut into portions by a small token budget, decoded side by
+    side by the scheduler (with and without CUDA graphs: the recurrent state must survive the
+    capture); the tokens are the plain model's greedy tokens."""
+    from hetero_serve_b200 import LLMEngine
+    case = mafuzen_case
+    prompts = [case.tokens(n, 200 + n) for n in (37, 5, 18)]
+    eng = LLMEngine(case.dir, dtype="float32", num_blocks=24, max_batch=4, max_prefill_tokens=16,
+                    policy="mixed", cuda_graphs=graphs, device=DEV)
+    got = eng.generate(prompts, max_new_tokens=12)
+    for p, g in zip(prompts, got):
+        want, margins = _greedy(case, p, 12)
+        for i, (a, b, m) in enumerate(zip(g, want, margins)):
+            if m < 1e-3:
+                break                                         # a close call: stop comparing
+            assert a == b, (len(p), i, g, want)
+    eng.runner.manager.check()
+
+
+def test_command_line_runs_a_preset():
+    out = subprocess.run([sys.executable, "-m", "hetero_serve_b200", "--model", "mafuzen-tiny",
+                          "--random-prompts", "2:12", "--max-new-tokens", "4"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
