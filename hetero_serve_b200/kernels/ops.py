@@ -233,6 +233,8 @@ def _declare(lib) -> None:
         "hs_span_prepare": [P, P, P, I, I, I, I, P, I, I, P, P, I, I, I, I, I, I, F, I, I, I, P, P],
         "hs_span_attention": [P, P, P, P, I, I, P, P, P, P, I, I, F, I, I, I, I, I, I, I, F, I, I,
                               I, P, P, P, P],
+        "hs_span_attention_prefill": [P, P, P, P, I, I, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I,
+                                      F, I, P, P],
         "hs_layernorm_add": [P, P, P, P, F, P, P, P, F, I, I, I, P],
         "hs_learned_act_xielu": [P, P, ctypes.c_longlong, F, F, I, P],
         "hs_scale_softcap": [P, ctypes.c_longlong, F, F, P],
@@ -1962,8 +1964,7 @@ class CudaOps:
         num_pages = pool.numel() // per_page
         listed = head = None
         if (plan is not None and plan.tile_cap > 0 and out.dtype == torch.bfloat16
-                and self.tensor_cores and self.span_mma and plan.n_rows >= T
-                and hasattr(self.lib, "hs_span_attention_prefill")):
+                and self.tensor_cores and self.span_mma and plan.n_rows >= T):
             d = plan.data
             code = self.lib.hs_span_attention_prefill(
                 _ptr(out), _ptr(q), _ptr(pool), _ptr(table), table.shape[1], num_pages,

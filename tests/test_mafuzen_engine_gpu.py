@@ -21,7 +21,9 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 # relative root-mean-square error of a row of logits: float32 sums of a few hundred terms;
 # bfloat16 rounds the rows the projections read and the cache rows to 8 bits
-TOL = {"float32": 3e-5, "bfloat16": 6e-2}
+# (the layer norms behind the sublayers take the mean off rows of 40 numbers: the plain twins on
+# float32 rows are as far from the float64 model, 6e-5 on the second case)
+TOL = {"float32": 1e-4, "bfloat16": 6e-2}
 
 
 def _bound(errs, dtype):
@@ -179,7 +181,9 @@ def test_a_far_key_under_the_slope(mafuzen_planted, dtype, how):
             res = rn.step([StepEntry(rid, t[cut:], want=[n - cut - 1])])
         rn.close(rid)
         err = rc.rms_error(res.logits[-1].cpu(), case.logits(t, dtype)[-1])
-        assert err < TOL[dtype], (at, n, err)
+        # a lost key moves these rows by 0.6 to 1.6; the rounded scores of a softmax this sharp
+        # by up to 0.08 in bfloat16
+        assert err < (0.15 if dtype == "bfloat16" else TOL[dtype]), (at, n, err)
 
 
 def test_long_decoding(mafuzen_cases):
