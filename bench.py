@@ -897,7 +897,8 @@ def main() -> int:
     ap.add_argument("--compare", nargs="?", const="pedorax-1k,pedorax-2k", default="",
                     help="instead of the default workload: named configurations of another "
                          "architecture (default pedorax-1k,pedorax-2k; also putelix-1k, "
-                         "putelix-2k, roritar-1k, roritar-2k), each beside GPT-2 at equal "
+                         "putelix-2k, roritar-1k, roritar-2k, mafuzen-1k, mafuzen-2k), each "
+                         "beside GPT-2 at equal "
                          "width, depth and vocabulary: prefill and decode throughput and every "
                          "operation of a step against its roofline")
     ap.add_argument("--one-step", dest="one_step", default="", choices=["", "decode", "prefill"],

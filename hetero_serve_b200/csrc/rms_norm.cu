@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(RMS_THREADS)
 rms_norm_add_kernel(float* __restrict__ x, TH* __restrict__ h, const float* __restrict__ a,
                     const float* __restrict__ wa, const float* __restrict__ b,
                     const float* __restrict__ wb, float mix, const float* __restrict__ w,
-                    int width, float eps_in, float eps) {
+                    int width, float eps_in, float eps, const float* __restrict__ ln_g,
+                    const float* __restrict__ ln_b, float ln_eps) {
   extern __shared__ float s_y[];                       // [width]
   __shared__ float s_part[RMS_THREADS / 32];
   pdl_trigger();
@@ -91,8 +92,23 @@ rms_norm_add_kernel(float* __restrict__ x, TH* __restrict__ h, const float* __re
   for (int e = threadIdx.x; e < width; e += RMS_THREADS) {
     const float v = xr[e] + (w ? s_y[e] * r * w[e] : s_y[e]);
     xr[e] = v;
-    if (h) h[row + e] = from_f<TH>(v);
+    if (ln_g) s_y[e] = v;                              // read back below by this thread alone
+    else if (h) h[row + e] = from_f<TH>(v);
   }
+  if (ln_g == nullptr || h == nullptr) return;
+  // h = the layer norm of the new row (the norm in front of the sublayer that runs next): the
+  // mean first, then the mean of the squared deviations
+  float sm = 0.f;
+  for (int e = threadIdx.x; e < width; e += RMS_THREADS) sm += s_y[e];
+  const float mean = block_sum(sm, s_part) / (float)width;
+  float sq = 0.f;
+  for (int e = threadIdx.x; e < width; e += RMS_THREADS) {
+    const float d = s_y[e] - mean;
+    sq = fmaf(d, d, sq);
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(sq, s_part) / (float)width + ln_eps);
+  for (int e = threadIdx.x; e < width; e += RMS_THREADS)
+    h[row + e] = from_f<TH>(fmaf((s_y[e] - mean) * rstd, ln_g[e], ln_b ? ln_b[e] : 0.f));
 }
 
 __global__ void cast_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ x,
@@ -138,11 +154,13 @@ HS_EXPORT int hs_rms_norm(void* out, const float* x, const float* w, const int* 
   return e == cudaSuccess ? HS_OK : (int)e;
 }
 
-// h_dtype: the type of the optional copy `h` (ignored when h is null).
+// h_dtype: the type of the optional copy `h` (ignored when h is null).  With ln_g (and ln_b or
+// null), h receives the layer norm of the new rows instead of the rows themselves.
 HS_EXPORT int hs_rms_norm_add(float* x, void* h, const float* a, const float* wa, const float* b,
                               const float* wb, float mix, const float* w, int n_rows, int width,
-                              float eps_in, float eps, int h_dtype, void* stream) {
-  if (!x || !a || (b && (!wa || !wb))) return HS_ERR_ARGUMENT;
+                              float eps_in, float eps, int h_dtype, const float* ln_g,
+                              const float* ln_b, float ln_eps, void* stream) {
+  if (!x || !a || (b && (!wa || !wb)) || (ln_g && !h)) return HS_ERR_ARGUMENT;
   if (width <= 0) return HS_ERR_UNSUPPORTED;
   if (n_rows <= 0) return HS_OK;
   const size_t smem = (size_t)width * sizeof(float);
@@ -154,13 +172,13 @@ HS_EXPORT int hs_rms_norm_add(float* x, void* h, const float* a, const float* wa
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     e = hs_launch(k, dim3(n_rows), dim3(hs::RMS_THREADS), smem, st, hs_pdl_enabled(), x,
-                  (__nv_bfloat16*)h, a, wa, b, wb, mix, w, width, eps_in, eps);
+                  (__nv_bfloat16*)h, a, wa, b, wb, mix, w, width, eps_in, eps, ln_g, ln_b, ln_eps);
   } else if (!h || h_dtype == HS_DT_F32) {
     auto k = hs::rms_norm_add_kernel<float>;
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     e = hs_launch(k, dim3(n_rows), dim3(hs::RMS_THREADS), smem, st, hs_pdl_enabled(), x,
-                  (float*)h, a, wa, b, wb, mix, w, width, eps_in, eps);
+                  (float*)h, a, wa, b, wb, mix, w, width, eps_in, eps, ln_g, ln_b, ln_eps);
   } else {
     return HS_ERR_UNSUPPORTED;
   }

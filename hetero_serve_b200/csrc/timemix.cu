@@ -4,7 +4,7 @@
 //   token_shift_mix    out[s][t] = x[t] + (x'[t] - x[t]) * mu[s] for every stream s, with x' the
 //                      row before (the slot's kept row for a request's first row of the step);
 //                      the block of a request's first row also keeps the step's last row
-//   timemix_decay      w = exp(-exp(W2 tanh(low) + w0)), float32
+//   timemix_decay      w = exp(-exp(W2 tanh(low) + w0)), float32, W2 handed in transposed
 //   timemix_recurrence per (request, head, group of value columns), token after token on the
 //                      float32 state S [dim, dim] of the request's slot:
 //                          o = (S + diag(u) k v^T)^T r ;   S <- diag(w) S + k v^T
@@ -60,22 +60,37 @@ token_shift_mix_kernel(T* __restrict__ out, const T* __restrict__ x, const float
   }
 }
 
+// w2t is the second matrix transposed, [rank][channels]: the threads of a block read a row of it
+// side by side, once for DK_TOK tokens.  Every (token, channel) sum runs over the inner index in
+// order, whatever the batch.
+constexpr int DK_TOK = 8;
 __global__ void __launch_bounds__(256)
 timemix_decay_kernel(float* __restrict__ out, const float* __restrict__ low,
-                     const float* __restrict__ w2, const float* __restrict__ w0, int channels,
-                     int rank) {
-  extern __shared__ float s_low[];                  // [rank]: tanh of the token's inner row
+                     const float* __restrict__ w2t, const float* __restrict__ w0, int n_tokens,
+                     int channels, int rank) {
+  extern __shared__ float s_low[];                  // [DK_TOK][rank]: tanh of the tokens' inner rows
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x;
-  for (int j = threadIdx.x; j < rank; j += blockDim.x) s_low[j] = tanhf(low[(size_t)t * rank + j]);
+  const int t0 = blockIdx.x * DK_TOK;
+  const int here = min(DK_TOK, n_tokens - t0);
+  for (int e = threadIdx.x; e < here * rank; e += blockDim.x)
+    s_low[e] = tanhf(low[(size_t)t0 * rank + e]);
+  for (int e = here * rank + threadIdx.x; e < DK_TOK * rank; e += blockDim.x) s_low[e] = 0.f;
   __syncthreads();
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-    const float* row = w2 + (size_t)c * rank;
-    float acc = 0.f;
-    for (int j = 0; j < rank; ++j) acc = fmaf(row[j], s_low[j], acc);
-    out[(size_t)t * channels + c] = expf(-expf(acc + w0[c]));
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  float acc[DK_TOK];
+#pragma unroll
+  for (int u = 0; u < DK_TOK; ++u) acc[u] = 0.f;
+  for (int j = 0; j < rank; ++j) {
+    const float wv = w2t[(size_t)j * channels + c];
+#pragma unroll
+    for (int u = 0; u < DK_TOK; ++u) acc[u] = fmaf(wv, s_low[u * rank + j], acc[u]);
   }
+  const float b = w0[c];
+#pragma unroll
+  for (int u = 0; u < DK_TOK; ++u)
+    if (u < here) out[(size_t)(t0 + u) * channels + c] = expf(-expf(acc[u] + b));
 }
 
 // ---------------------------------------------------------------------------------------
@@ -313,14 +328,16 @@ HS_EXPORT int hs_token_shift_mix(void* out, const void* x, const float* mu, floa
   return e == cudaSuccess ? HS_OK : (int)e;
 }
 
-HS_EXPORT int hs_timemix_decay(float* out, const float* low, const float* w2, const float* w0,
+HS_EXPORT int hs_timemix_decay(float* out, const float* low, const float* w2t, const float* w0,
                                int n_tokens, int channels, int rank, void* stream) {
-  if (!out || !low || !w2 || !w0) return HS_ERR_ARGUMENT;
-  if (channels <= 0 || rank <= 0 || rank > 8192) return HS_ERR_UNSUPPORTED;
+  if (!out || !low || !w2t || !w0) return HS_ERR_ARGUMENT;
+  if (channels <= 0 || rank <= 0 || rank > 1024) return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
-  cudaError_t e = hs_launch(hs::timemix_decay_kernel, dim3(n_tokens), dim3(256),
-                            (size_t)rank * sizeof(float), (cudaStream_t)stream, hs_pdl_enabled(),
-                            out, low, w2, w0, channels, rank);
+  const dim3 grid((n_tokens + hs::DK_TOK - 1) / hs::DK_TOK, (channels + 255) / 256);
+  if (grid.y > 65535) return HS_ERR_TOO_LARGE;
+  cudaError_t e = hs_launch(hs::timemix_decay_kernel, grid, dim3(256),
+                            (size_t)hs::DK_TOK * rank * sizeof(float), (cudaStream_t)stream,
+                            hs_pdl_enabled(), out, low, w2t, w0, n_tokens, channels, rank);
   return e == cudaSuccess ? HS_OK : (int)e;
 }
 

@@ -147,12 +147,50 @@ def _flops_and_bytes(name, args, kw, batch):
             h, wr = args[2], args[3]
             return 2 * h.shape[0] * wr.shape[0] * wr.shape[1], _nbytes(h, wr)
         if name == "moe_experts":
-            x, _y, h, wg = args[:4]
+            x, _y, h, wg, wu = args[:5]
             idx = args[6]
-            E, width, ff = wg.shape
+            E, width, ff = wu.shape
+            mats = 3 if wg is not None else 2          # an expert without a gate: up and down
             pairs = idx.shape[0] * idx.shape[1]
-            touched = min(E, pairs) * 3 * width * ff * wg.element_size()
-            return 2 * pairs * 3 * width * ff, _nbytes(h) + 2 * _nbytes(x) + touched
+            touched = min(E, pairs) * mats * width * ff * wu.element_size()
+            return 2 * pairs * mats * width * ff, _nbytes(h) + 2 * _nbytes(x) + touched
+        if name == "moe_route_table":
+            return 0, 3 * _nbytes(args[0])
+        if name == "span_prepare":
+            q_out, pool, proj = args[:3]
+            rows = q_out.shape[0] * kw["n_kv_heads"] * (kw["head_dim"] + kw["value_dim"])
+            return 0, _nbytes(q_out) + proj.numel() * 4 + (rows * pool.element_size()
+                                                           if kw["writes"] else 0)
+        if name == "span_attention":
+            out, q, pool = args[:3]
+            H, G, D, V = kw["n_heads"], kw["n_kv_heads"], kw["head_dim"], kw["value_dim"]
+            win, keep = kw["window"], kw["keep_first"]
+            seen = rows = 0
+            for start, n in batch:
+                for i in range(start, start + n):
+                    seen += min(i + 1, win) + min(keep, max(0, i - win + 1)) if win else i + 1
+                last = start + n - 1
+                lo = max(0, start - win + 1) if win else 0
+                rows += last + 1 - lo + min(keep, lo)    # distinct cache rows the portion reads
+            gate = out.numel() * 4 if kw.get("gate") is not None else 0
+            return (2 * H * (D + V) * seen,
+                    _nbytes(out, q) + gate + rows * G * (D + V) * pool.element_size())
+        if name == "token_shift_mix":
+            out, x = args[:2]
+            return 0, _nbytes(out, x)
+        if name == "timemix_decay":
+            out, low, w2t = args[:3]
+            return 2 * out.numel() * low.shape[1], _nbytes(out, low, w2t)
+        if name == "timemix_recurrence":
+            o, state = args[:2]
+            H, D = kw["heads"], kw["dim"]
+            live = len([1 for _s, n in batch if n > 0])
+            return 6 * o.shape[0] * H * D * D, 5 * _nbytes(o) + 2 * live * H * D * D * 4
+        if name == "head_norm_gate":
+            out, o = args[:2]
+            return 0, _nbytes(out, o) + (o.numel() * 4 if args[3] is not None else 0)
+        if name == "gather_mul":
+            return 0, 2 * _nbytes(args[0]) + _nbytes(args[1])
         if name == "layernorm_add":
             x, y = args[:2]
             return 0, 2 * _nbytes(x) + _nbytes(y, kw.get("out"))

@@ -214,7 +214,7 @@ def _declare(lib) -> None:
         "hs_moe_experts": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P, P],
         "hs_moe_route_top": [P, P, P, P, P, P, I, I, I, I, I, P, P],
         "hs_rms_norm": [P, P, P, P, I, I, F, I, P, I, I, I, P],
-        "hs_rms_norm_add": [P, P, P, P, P, P, F, P, I, I, F, F, I, P],
+        "hs_rms_norm_add": [P, P, P, P, P, P, F, P, I, I, F, F, I, P, P, F, P],
         "hs_cast_rows": [P, P, ctypes.c_longlong, P],
         "hs_gated_act": [P, P, P, P, P, I, I, I, I, I, P],
         "hs_qk_prepare": [P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, I, I, I, I, P, P],
@@ -1383,11 +1383,12 @@ class CudaOps:
                f"rms_norm(width={width})")
 
     def rms_norm_add(self, x, a, weight, eps, h=None, b=None, wa=None, wb=None, mix=0.5,
-                     eps_in=None):
+                     eps_in=None, ln=None):
         """The norm of a sublayer's output added into the stream: with y = a, or, given a second
         input, y = mix * (rms(a) * wa + rms(b) * wb) (those two norms with ``eps_in``, by
         default ``eps``):  x += rms(y) * weight, or x += y when ``weight`` is None.  ``h`` (of
-        the compute type), if given, receives a copy of the new x."""
+        the compute type), if given, receives a copy of the new x, or with ``ln=(gamma, beta or
+        None, eps)`` the layer norm of the new x."""
         _want(x, "x", torch.float32, 2)
         _want(a, "a", torch.float32, 2)
         n, width = x.shape
@@ -1407,11 +1408,20 @@ class CudaOps:
             _want(h, "h", _FLOATS, 2)
             if tuple(h.shape) != (n, width):
                 raise KernelError("rms_norm_add: h has another shape than x")
+        ln_g = None
+        if ln is not None:
+            if h is None:
+                raise KernelError("rms_norm_add: the layer norm of the new rows goes to h")
+            ln_g = _want(ln[0], "ln gamma", torch.float32, 1)
+            if ln_g.shape[0] != width or (ln[1] is not None and ln[1].shape[0] != width):
+                raise KernelError("rms_norm_add: the layer norm's parameters do not fit")
         self.launches += 1
         _check(self.lib.hs_rms_norm_add(_ptr(x), _ptr(h), _ptr(a), _ptr(wa), _ptr(b), _ptr(wb),
                                         float(mix), _ptr(weight), n, width,
                                         float(eps if eps_in is None else eps_in), float(eps),
-                                        _DT[h.dtype] if h is not None else 0, self._stream()),
+                                        _DT[h.dtype] if h is not None else 0, _ptr(ln_g),
+                                        _ptr(ln[1]) if ln is not None else None,
+                                        float(ln[2]) if ln is not None else 0.0, self._stream()),
                f"rms_norm_add(width={width})")
 
     def cast_rows(self, out, x):
@@ -1803,18 +1813,19 @@ class CudaOps:
             _ptr(tok_req), _ptr(req_start), _ptr(req_len), _ptr(req_slot), T, W, S,
             _DT[out.dtype], self._stream()), "token_shift_mix")
 
-    def timemix_decay(self, out, low, w2, w0):
-        """out[t, c] = exp(-exp(sum_j w2[c, j] tanh(low[t, j]) + w0[c])), all float32."""
+    def timemix_decay(self, out, low, w2t, w0):
+        """out[t, c] = exp(-exp(sum_j w2t[j, c] tanh(low[t, j]) + w0[c])), all float32; ``w2t``
+        is the second matrix of the decay transposed, [inner, channels]."""
         _want(out, "out", torch.float32, 2)
         _want(low, "low", torch.float32, 2)
-        _want(w2, "w2", torch.float32, 2)
+        _want(w2t, "w2t", torch.float32, 2)
         _want(w0, "w0", torch.float32, 1)
         T, C = out.shape
         rank = low.shape[1]
-        if low.shape[0] < T or tuple(w2.shape) != (C, rank) or w0.shape[0] != C:
+        if low.shape[0] < T or tuple(w2t.shape) != (rank, C) or w0.shape[0] != C:
             raise KernelError("timemix_decay: shapes do not fit")
         self.launches += 1
-        _check(self.lib.hs_timemix_decay(_ptr(out), _ptr(low), _ptr(w2), _ptr(w0), T, C, rank,
+        _check(self.lib.hs_timemix_decay(_ptr(out), _ptr(low), _ptr(w2t), _ptr(w0), T, C, rank,
                                          self._stream()), f"timemix_decay(rank={rank})")
 
     def timemix_recurrence(self, o, state, r, k, v, w, u, req_start, req_len, req_slot, *, heads,

@@ -50,10 +50,11 @@ class TimeMix(Mixer):
         p, t = self.p, tensors
         self.mu = torch.stack([t[p + "mu." + s] for s in STREAMS]).contiguous()     # [5, W]
         self.w_r, self.w_k, self.w_v, self.w_g = (t[p + s] for s in ("r", "k", "v", "g"))
-        self.w1, self.w2, self.w0 = t[p + "w1"], t[p + "w2"], t[p + "w0"]
+        self.w1, self.w0 = t[p + "w1"], t[p + "w0"]
+        self.w2t = t[p + "w2"].t().contiguous()                # [inner, channels]: read side by side
         self.u, self.norm_w, self.w_out = t[p + "u"].reshape(-1).contiguous(), t[p + "norm"], t[p + "o"]
         self.rank = self.w1.shape[0]
-        if self.w2.shape[1] != self.rank:
+        if self.w2t.shape[0] != self.rank:
             raise ValueError("the two matrices of the decay do not share their inner size")
 
     def state_shape(self):
@@ -72,7 +73,7 @@ class TimeMix(Mixer):
         low = ctx.buffer("timemix_low", (T, self.rank), torch.float32)
         ops.linear(low, mixes[4], self.w1)
         decay = ctx.buffer("timemix_decay", (T, hd), torch.float32)
-        ops.timemix_decay(decay, low, self.w2, self.w0)
+        ops.timemix_decay(decay, low, self.w2t, self.w0)
         o = ctx.buffer("timemix_o", (T, hd), torch.float32)
         ops.timemix_recurrence(o, state, rkvg[0], rkvg[1], rkvg[2], decay, self.u,
                                ctx.req_start, ctx.req_len, ctx.req_slot, heads=self.H,

@@ -7,7 +7,8 @@ the stream, and the result is RMS-normed and added to the stream.
 
 It runs as the last part of a block (slot ``side`` of the ``sandwich_norm`` arrangement).  The
 two products are ordinary linears; the gather-and-multiply between them is one launch and the
-norm with the residual sum is the launch every RMS norm behind a sublayer uses, float32.
+norm with the residual sum is the launch every RMS norm behind a sublayer uses, float32; it
+also forms the layer norm in front of the block that runs next.
 """
 
 from __future__ import annotations
@@ -43,7 +44,11 @@ class TokenSideInput(FeedForward):
         self.table, self.w_gate, self.w_proj, self.w_norm = (tensors[tb], tensors[gw],
                                                              tensors[pw], tensors[nw])
 
-    def forward(self, ctx, h, x):
+    forms_next_norm = True       # its last launch can form the norm of the block that runs next
+
+    def forward(self, ctx, h, x, then=None):
+        """``then=(norm, out)``: ``out`` also receives ``norm(x)`` of the new rows; a layer norm
+        is formed by the launch that adds into the stream."""
         ops, T = ctx.ops, x.shape[0]
         if ctx.dtype == torch.float32:
             src = x
@@ -57,7 +62,14 @@ class TokenSideInput(FeedForward):
                        feedback=ctx.feedback)
         y = ctx.buffer("side_out", (T, self.width), torch.float32)
         ops.linear(y, ge, self.w_proj, None)
+        nxt = then[0] if then is not None else None
+        if nxt is not None and nxt.kind == "layernorm":
+            ops.rms_norm_add(x, y, self.w_norm, self.eps, h=then[1],
+                             ln=(nxt.weight, nxt.bias, nxt.eps))
+            return
         ops.rms_norm_add(x, y, self.w_norm, self.eps)
+        if nxt is not None:
+            nxt.forward(ctx, then[1], x)
 
 
 register_feed_forward("token_side_input", TokenSideInput)

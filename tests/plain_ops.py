@@ -379,7 +379,7 @@ class PlainOps:
         out.copy_(v.to(out.dtype))
 
     def rms_norm_add(self, x, a, weight, eps, h=None, b=None, wa=None, wb=None, mix=0.5,
-                     eps_in=None):
+                     eps_in=None, ln=None):
         n = x.shape[0]
         y = a[:n].to(self.cd)
         if b is not None:
@@ -389,7 +389,10 @@ class PlainOps:
         if weight is not None:
             y = self._rms(y, eps) * weight.to(self.cd)
         x.copy_((x.to(self.cd) + y).to(x.dtype))
-        if h is not None:
+        if h is not None and ln is not None:
+            beta = ln[1] if ln[1] is not None else torch.zeros_like(ln[0])
+            h.copy_(self._ln(x.to(self.cd), ln[0], beta, ln[2]).to(h.dtype))
+        elif h is not None:
             h.copy_(x.to(h.dtype))
 
     def cast_rows(self, out, x):
@@ -721,9 +724,9 @@ class PlainOps:
                 prev = cur
             state[slot, state_offset:state_offset + W] = prev.to(state.dtype)
 
-    def timemix_decay(self, out, low, w2, w0):
+    def timemix_decay(self, out, low, w2t, w0):
         n = out.shape[0]
-        lw = torch.tanh(low[:n].to(self.cd)) @ w2.to(self.cd).T + w0.to(self.cd)
+        lw = torch.tanh(low[:n].to(self.cd)) @ w2t.to(self.cd) + w0.to(self.cd)
         out.copy_(torch.exp(-torch.exp(lw)).to(out.dtype))
 
     def timemix_recurrence(self, o, state, r, k, v, w, u, req_start, req_len, req_slot, *,

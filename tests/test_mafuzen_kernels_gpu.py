@@ -318,7 +318,7 @@ def test_time_mixing_in_portions_and_batches(ops, H, D, rank):
     want = {r: P.time_mix({"heads": H, "dim": D}, w, "m.", x.double(), eps) for r, x in rows.items()}
     state = torch.zeros(2, hd * D + 3, device=DEV)
     slot = {"a": 1, "b": 0}
-    w2, w0, u, nw = dev(w["m.w2"].float(), w["m.w0"].float(), w["m.u"].float().reshape(-1),
+    w2, w0, u, nw = dev(w["m.w2"].float().t(), w["m.w0"].float(), w["m.u"].float().reshape(-1),
                         w["m.norm"].float())
     plan = [[("a", 3)], [("a", 1), ("b", 2)], [("b", 40), ("a", 1)], [("a", 66)], [("a", 1), ("b", 1)],
             [("b", 7), ("a", 48)]]
