@@ -2,7 +2,8 @@
 // launch the layer norm of the new rows for the sublayer that follows:
 //
 //   x   += (y - mean(y)) / sqrt(var(y) + eps) * g + b
-//   out  = (x - mean(x)) / sqrt(var(x) + eps2) * g2 + b2          (optional)
+//   out  = (x - mean(x)) / sqrt(var(x) + eps2) * g2 + b2          (optional; without g2: out = x,
+//                                                                   the new rows in out's type)
 //
 // One block per row, the row in shared memory; mean first, then the mean of the squared
 // deviations, each summed in an order fixed by the width: a row's result does not depend on its
@@ -59,8 +60,9 @@ layernorm_add_kernel(float* __restrict__ x, const float* __restrict__ y,
     x[row + e] = v;
     s_row[e] = v;
     s2 += v;
+    if (out != nullptr && g2 == nullptr) out[row + e] = from_f<TO>(v);   // the new rows as they are
   }
-  if (out == nullptr) return;
+  if (out == nullptr || g2 == nullptr) return;
   const float mean2 = lna_block_sum(s2, s_part) * inv_w;
   float ss2 = 0.f;
   for (int e = threadIdx.x; e < width; e += LNA_THREADS) {
@@ -100,7 +102,7 @@ __global__ void scale_softcap_kernel(float* __restrict__ t, long long n, float s
 HS_EXPORT int hs_layernorm_add(float* x, const float* y, const float* g, const float* b, float eps,
                                void* out, const float* g2, const float* b2, float eps2,
                                int n_rows, int width, int out_dtype, void* stream) {
-  if (!x || !y || !g || (out && !g2)) return HS_ERR_ARGUMENT;
+  if (!x || !y || !g) return HS_ERR_ARGUMENT;
   if (width <= 0) return HS_ERR_UNSUPPORTED;
   if (n_rows <= 0) return HS_OK;
   const size_t smem = (size_t)width * sizeof(float);

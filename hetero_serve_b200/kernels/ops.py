@@ -1580,7 +1580,7 @@ class CudaOps:
                       out_eps=None):
         """x += LayerNorm(y) * gamma + beta for the float32 rows of ``y`` (``beta`` may be
         None); with ``out``, also out = LayerNorm(new x) * out_gamma + out_beta: the rows the
-        next sublayer takes, in the compute type."""
+        next sublayer takes, in the compute type (without ``out_gamma``: out = new x)."""
         _want(x, "x", torch.float32, 2)
         _want(y, "y", torch.float32, 2)
         _want(gamma, "gamma", torch.float32, 1)
@@ -1594,8 +1594,8 @@ class CudaOps:
                     raise KernelError(f"layernorm_add: {name} has another width")
         if out is not None:
             _want(out, "out", _FLOATS, 2)
-            if tuple(out.shape) != (n, width) or out_gamma is None:
-                raise KernelError("layernorm_add: out needs x's shape and a weight")
+            if tuple(out.shape) != (n, width):
+                raise KernelError("layernorm_add: out needs x's shape")
         self.launches += 1
         _check(self.lib.hs_layernorm_add(
             _ptr(x), _ptr(y), _ptr(gamma), _ptr(beta), float(eps), _ptr(out), _ptr(out_gamma),

@@ -186,18 +186,25 @@ class SandwichNormBlock(Block):
             ahead = None                      # the stream still changes behind the last norm
         ctx.normed_ahead = ahead is not None
         last = None if self.side is not None else ahead
+        # a side part that reads the stream in the compute type gets its copy from the launch of
+        # the last norm (a 16-bit engine; in float32 it reads the stream itself)
+        more = {}
+        if self.side is not None and ctx.dtype != torch.float32 \
+                and getattr(self.side, "takes_stream_copy", False):
+            more["h"] = ctx.buffer("side_stream_copy", (T, W), ctx.dtype)
         out = OutputNormBlock._run(self.mixer, ctx, h, y, cache)
         if not self.has_ff:
-            self.norm1b.add_normed(ctx, x, out, then=last)
+            self.norm1b.add_normed(ctx, x, out, then=last, **more)
         else:
             self.norm1b.add_normed(ctx, x, out, then=(self.norm2, h))
             out = OutputNormBlock._run(self.feed_forward, ctx, h, y)
-            self.norm2b.add_normed(ctx, x, out, then=last)
+            self.norm2b.add_normed(ctx, x, out, then=last, **more)
         if self.side is not None:
+            extra = {"x_copy": more["h"]} if more else {}
             if side_ahead:
-                self.side.forward(ctx, h, x, then=ahead)
+                self.side.forward(ctx, h, x, then=ahead, **extra)
             else:
-                self.side.forward(ctx, h, x)
+                self.side.forward(ctx, h, x, **extra)
 
 
 _ARRANGEMENTS: dict[str, Callable[[LayerSpec], Block]] = {"pre_norm": PreNormBlock,

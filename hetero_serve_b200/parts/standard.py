@@ -96,7 +96,11 @@ class LayerNorm(Norm):
     def add_normed(self, ctx, x, y, h=None, then=None):
         """x += norm(y) for a float32 block ``y``.  With ``then=(norm, out)``, ``out`` also
         receives ``norm(x)`` of the new rows (another layer norm's output, for the sublayer
-        that follows)."""
+        that follows); with ``h`` (and no ``then``) it receives the new rows of x themselves
+        in the compute type."""
+        if then is None and h is not None:
+            ctx.ops.layernorm_add(x, y, self.weight, self.bias, self.eps, out=h)
+            return
         if then is not None and isinstance(then[0], LayerNorm):
             nxt, out = then
             ctx.ops.layernorm_add(x, y, self.weight, self.bias, self.eps, out=out,

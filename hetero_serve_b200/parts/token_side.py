@@ -45,13 +45,17 @@ class TokenSideInput(FeedForward):
                                                              tensors[pw], tensors[nw])
 
     forms_next_norm = True       # its last launch can form the norm of the block that runs next
+    takes_stream_copy = True     # in a 16-bit engine it reads a copy of the stream the caller has
 
-    def forward(self, ctx, h, x, then=None):
+    def forward(self, ctx, h, x, then=None, x_copy=None):
         """``then=(norm, out)``: ``out`` also receives ``norm(x)`` of the new rows; a layer norm
-        is formed by the launch that adds into the stream."""
+        is formed by the launch that adds into the stream.  ``x_copy``: the stream's rows in the
+        compute type, when the launch before left them (else they are cast here)."""
         ops, T = ctx.ops, x.shape[0]
         if ctx.dtype == torch.float32:
             src = x
+        elif x_copy is not None:
+            src = x_copy
         else:
             src = ctx.buffer("side_in", (T, self.width), ctx.dtype)
             ops.cast_rows(src, x)

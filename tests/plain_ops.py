@@ -487,7 +487,9 @@ class PlainOps:
         n = x.shape[0]
         new = x.to(self.cd) + self._ln(y[:n].to(self.cd), gamma, beta, eps)
         x.copy_(new.to(x.dtype))
-        if out is not None:
+        if out is not None and out_gamma is None:
+            out.copy_(x.to(out.dtype))
+        elif out is not None:
             out.copy_(self._ln(x.to(self.cd), out_gamma, out_beta, out_eps).to(out.dtype))
 
     def learned_act(self, out, z, act, values):
