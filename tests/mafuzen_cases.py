@@ -27,8 +27,8 @@ def _att(heads, kv_heads, dim, vdim, scale=None, kv_from=None):
     return m
 
 
-def _par(heads, kv_heads, dim, window, keep_first, r_heads, r_dim, scale=None, left_scale=0.6,
-         right_scale=1.1):
+def _par(heads, kv_heads, dim, window, keep_first, r_heads, r_dim, scale=None, left_scale=0.7,
+         right_scale=1.3):
     left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
             "scale": scale if scale is not None else 3.0 / math.sqrt(dim)}
     if window:
@@ -65,7 +65,7 @@ CASE_A = _model(311, 44, 1e-5, [
     _layer("attention", _att(6, 2, 12, 20, scale=0.4), _moe(28, 5, 2, shared=36)),
     _layer("parallel", _par(4, 2, 12, 21, 3, 3, 12), None),
     _layer("attention", _att(6, 2, 12, 20, kv_from=1), _moe(20, 4, 3)),
-    _layer("retention", _ret(2, 16, 8, [0.96875, 0.75], rot_dims=16, base=1e6),
+    _layer("retention", _ret(2, 16, 8, [0.9375, 0.75], rot_dims=16, base=5e5),
            {"kind": "dense", "ff": 40}),
     _layer("attention", _att(6, 2, 12, 20, scale=0.2, kv_from=1), None),
 ], scale=6.5, side=5)
