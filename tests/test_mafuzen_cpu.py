@@ -365,3 +365,37 @@ def test_the_parts_in_another_arrangement(mafuzen_cases):
     x = x + P.dense_ff(w, "l0.mlp.", ln("l0.norm2", x))
     want = ln("final.norm", x) @ w["embed"].T
     assert (got - want[[13, 59]]).abs().max() < TOL
+
+
+@pytest.mark.parametrize("which", ["retention only", "pairs without a mask", "windows that differ",
+                                   "a chain of readers", "one layer"])
+def test_other_orders_of_layers(which, tmp_path):
+    """Models of one kind of layer (no page group at all; no window), page groups that differ
+    only in their window or kept tokens, several readers of two writers, a single layer: mixed
+    batches with pages and slots used again against the plain model."""
+    import json
+    from hetero_serve_b200.weights import read_safetensors, write_model_dir
+    moe = mc._moe(16, 3, 2)
+    layers = {
+        "retention only": [mc._layer("retention", mc._ret(2, 8, 12, [0.9, 0.99], rot_dims=4, base=100.0),
+                                     {"kind": "dense", "ff": 64})] * 2,
+        "pairs without a mask": [mc._layer("parallel", mc._par(2, 1, 8, 0, 0, 1, 8), None)] * 2,
+        "windows that differ": [mc._layer("parallel", mc._par(2, 1, 8, 5, 0, 1, 8), None),
+                                mc._layer("parallel", mc._par(2, 1, 8, 9, 30, 1, 8), None),
+                                mc._layer("parallel", mc._par(2, 1, 8, 9, 0, 1, 8), moe)],
+        "a chain of readers": [mc._layer("attention", mc._att(4, 2, 8, 4, scale=0.3), moe),
+                               mc._layer("attention", mc._att(4, 2, 8, 4, kv_from=0), moe),
+                               mc._layer("attention", mc._att(2, 2, 8, 4), None),
+                               mc._layer("attention", mc._att(4, 2, 8, 4, kv_from=2), moe),
+                               mc._layer("attention", mc._att(2, 2, 8, 4, kv_from=0), moe)],
+        "one layer": [mc._layer("attention", mc._att(4, 2, 8, 4), None)],
+    }[which]
+    cfg = mc._model(90, 48, 1e-6, layers, scale=3.0, side=4 if which != "one layer" else 0)
+    folder = tmp_path / "model"
+    write_model_dir(folder, cfg, 1, "float32")
+    case = mc.Case(which, folder, json.loads((folder / "config.json").read_text()), 1)
+    reqs = {f"r{i}": case.tokens(n, 20 + i) for i, n in enumerate((70, 9, 33))}
+    steps, index, peak = traces.mixed(reqs, seed=1, max_live=2, sizes=(1, 2, 5, 1, 17, 3))
+    out = _replay(case, steps, tmp_path, max_tokens=peak, max_requests=2)
+    err, where = _worst(case, out, index, reqs)
+    assert err < TOL, (err, where)
