@@ -255,3 +255,32 @@ def test_command_line_runs_a_preset():
                           "--random-prompts", "2:12", "--max-new-tokens", "4"],
                          capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["retention only", "pairs without a mask", "a chain of readers"])
+def test_other_orders_of_layers(which, dtype, tmp_path):
+    """A model without any page group, one whose pairs have no window, several readers of two
+    writers: mixed batches with pages and slots used again against the plain model."""
+    import json
+    from hetero_serve_b200.weights import write_model_dir
+    moe = rc._moe(32, 4, 2)
+    layers = {
+        "retention only": [rc._layer("retention", rc._ret(2, 16, 24, [0.9, 0.99], rot_dims=8, base=100.0),
+                                     {"kind": "dense", "ff": 64})] * 2,
+        "pairs without a mask": [rc._layer("parallel", rc._par(2, 1, 16, 0, 0, 1, 16), None)] * 2,
+        "a chain of readers": [rc._layer("attention", rc._att(4, 2, 16, 8, scale=0.3), moe),
+                               rc._layer("attention", rc._att(4, 2, 16, 8, kv_from=0), moe),
+                               rc._layer("attention", rc._att(2, 2, 16, 8), None),
+                               rc._layer("attention", rc._att(4, 2, 16, 8, kv_from=2), moe),
+                               rc._layer("attention", rc._att(2, 2, 16, 8, kv_from=0), moe)],
+    }[which]
+    cfg = rc._model(90, 64, 1e-6, layers, scale=3.0, side=8)
+    folder = tmp_path / "model"
+    write_model_dir(folder, cfg, 1, "float32")
+    case = rc.Case(which, folder, json.loads((folder / "config.json").read_text()), 1)
+    reqs = {f"r{i}": case.tokens(n, 20 + i) for i, n in enumerate((70, 9, 33, 150))}
+    steps, index, peak = traces.mixed(reqs, seed=1, max_live=3)
+    out = _replay(case, dtype, steps, tmp_path, max_tokens=peak, max_requests=3)
+    err, where, n = _worst(case, dtype, out, index, reqs)
+    assert n > 10 and err < TOL[dtype], (err, where)
